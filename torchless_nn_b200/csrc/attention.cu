@@ -1,0 +1,387 @@
+// Fused attention: softmax(Q K^T / sqrt(hd) [+ causal mask]) V without materialising the score matrix.
+//
+// Input is the packed projection (B, T, 3d) produced by the QKV GEMM (columns [0,d) Q, [d,2d) K, [2d,3d) V; head h
+// at columns h*hd inside each third), so no head-major copy is ever made; output is written merged as (B, T, d).
+// The decoder mask of the reference (-1e9 above the diagonal, exp underflows to exactly 0 in float32) is applied as
+// an index comparison.
+//
+//  * bf16 path: flash-style kernel, 128 queries x 64 keys per step, 8 warps, operands staged with cp.async into
+//    XOR-swizzled shared memory, ldmatrix + mma.sync m16n8k16 (bf16 in, float32 accumulate), online softmax in
+//    registers with quad shuffles, exp2 with the 1/sqrt(hd) scale folded in.
+//  * float32 path: CUDA-core kernel in exact float32 arithmetic (one warp per query, keys across lanes) for the
+//    FP32/TF32 mode, where the shapes are small (T <= 128, hd 32) and operand rounding would eat the tolerance.
+#include "common.cuh"
+
+namespace {
+
+// ============================================================================================ bf16 flash kernel
+constexpr int FA_BM = 128;   // queries per CTA
+constexpr int FA_BN = 64;    // keys per step
+constexpr int FA_THREADS = 256;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    int bytes = valid ? 16 : 0;   // src-size 0 zero-fills the 16 destination bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD bf16; the chunk index is XOR-ed
+// with row bits so that the eight rows touched by one ldmatrix phase fall into distinct banks.
+template <int HD>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    constexpr int ROWB = HD * 2;
+    int sw = HD == 32 ? ((row >> 1) & 3) : (row & 7);
+    return (uint32_t)(row * ROWB + ((chunk ^ sw) << 4));
+}
+
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* dst_base, const __nv_bfloat16* src, long long row_stride, int row0,
+                                          int rows, int T) {
+    constexpr int CPR = HD / 8;   // 16-byte chunks per row
+    const uint32_t dst = smem_u32(dst_base);
+    for (int i = threadIdx.x; i < rows * CPR; i += FA_THREADS) {
+        int r = i / CPR, c = i % CPR;
+        int t = row0 + r;
+        bool ok = t < T;
+        const __nv_bfloat16* p = src + (long long)(ok ? t : 0) * row_stride + c * 8;
+        cp_async16(dst + swz<HD>(r, c), p, ok);
+    }
+}
+
+template <int HD, bool CAUSAL>
+__global__ void __launch_bounds__(FA_THREADS)
+flash_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, int T, int H, float scale_log2) {
+    constexpr int KSTEPS = HD / 16;       // k-steps of the S = Q K^T product
+    constexpr int DT = HD / 8;            // 8-wide output column tiles
+    constexpr int NT = FA_BN / 8;         // 8-wide key tiles per step
+    extern __shared__ __align__(128) uint8_t fa_smem[];
+    uint8_t* sQ = fa_smem;
+    uint8_t* sK = sQ + FA_BM * HD * 2;
+    uint8_t* sV = sK + 2 * FA_BN * HD * 2;
+
+    const int d = H * HD;
+    const long long row_stride = 3ll * d;
+    const int bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const int q_tile = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;   // longest causal tiles first
+    const int q0 = q_tile * FA_BM;
+    const __nv_bfloat16* qbase = qkv + (long long)b * T * row_stride + h * HD;
+    const __nv_bfloat16* kbase = qbase + d;
+    const __nv_bfloat16* vbase = qbase + 2 * d;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+    const int wrow0 = warp * 16;                     // first query row of this warp inside the tile
+
+    int kv_end = T;
+    if (CAUSAL) kv_end = min(T, q0 + FA_BM);
+    const int n_steps = (kv_end + FA_BN - 1) / FA_BN;
+
+    load_tile<HD>(sQ, qbase, row_stride, q0, FA_BM, T);
+    load_tile<HD>(sK, kbase, row_stride, 0, FA_BN, T);
+    load_tile<HD>(sV, vbase, row_stride, 0, FA_BN, T);
+    cp_async_commit();
+
+    uint32_t qf[KSTEPS][4];
+    float o[DT][4];
+#pragma unroll
+    for (int i = 0; i < DT; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY;     // running maxima (already multiplied by scale_log2) of rows g and g+8
+    float l0 = 0.f, l1 = 0.f;                 // running partial sums (this thread's columns only)
+
+    for (int j = 0; j < n_steps; j++) {
+        const int buf = j & 1;
+        if (j + 1 < n_steps) {
+            load_tile<HD>(sK + (buf ^ 1) * FA_BN * HD * 2, kbase, row_stride, (j + 1) * FA_BN, FA_BN, T);
+            load_tile<HD>(sV + (buf ^ 1) * FA_BN * HD * 2, vbase, row_stride, (j + 1) * FA_BN, FA_BN, T);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (j == 0) {
+            const uint32_t q_s = smem_u32(sQ);
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                int row = wrow0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                int chunk = ks * 2 + (lane >> 4);
+                ldmatrix_x4(q_s + swz<HD>(row, chunk), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+            }
+        }
+        const int key0 = j * FA_BN;
+        // A warp whose every query precedes every key of this step has nothing to add (causal only).
+        const bool active = !CAUSAL || key0 <= q0 + wrow0 + 15;
+        if (active) {
+            const uint32_t k_s = smem_u32(sK + buf * FA_BN * HD * 2);
+            const uint32_t v_s = smem_u32(sV + buf * FA_BN * HD * 2);
+            float s[NT][4];
+#pragma unroll
+            for (int i = 0; i < NT; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    int key = nt * 8 + (lane & 7) + (lane >> 4) * 8;
+                    int chunk = ks * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(k_s + swz<HD>(key, chunk), b0, b1, b2, b3);
+                    mma_bf16(s[nt], qf[ks], b0, b1);
+                    mma_bf16(s[nt + 1], qf[ks], b2, b3);
+                }
+            }
+            // masking: keys beyond the sequence end, and keys after the query for the decoder
+            const bool need_mask = (key0 + FA_BN > T) || (CAUSAL && key0 + FA_BN - 1 > q0 + wrow0);
+            if (need_mask) {
+                const int r0 = q0 + wrow0 + g, r1 = r0 + 8;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    int c = key0 + nt * 8 + tq * 2;
+                    bool dead0 = c >= T, dead1 = c + 1 >= T;
+                    if ((CAUSAL && c > r0) || dead0) s[nt][0] = -INFINITY;
+                    if ((CAUSAL && c + 1 > r0) || dead1) s[nt][1] = -INFINITY;
+                    if ((CAUSAL && c > r1) || dead0) s[nt][2] = -INFINITY;
+                    if ((CAUSAL && c + 1 > r1) || dead1) s[nt][3] = -INFINITY;
+                }
+            }
+            // online softmax
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0 * scale_log2), mn1 = fmaxf(m1, mx1 * scale_log2);
+            // a row with no live key yet keeps m = -inf; use 0 as the subtrahend there so exp2(-inf - 0) = 0
+            const float sub0 = mn0 == -INFINITY ? 0.f : mn0, sub1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float a0 = exp2f(m0 - sub0), a1 = exp2f(m1 - sub1);
+            m0 = mn0; m1 = mn1;
+            l0 *= a0; l1 *= a1;
+#pragma unroll
+            for (int i = 0; i < DT; i++) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+            uint32_t pf[NT / 2][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float p0 = exp2f(fmaf(s[nt][0], scale_log2, -sub0));
+                float p1 = exp2f(fmaf(s[nt][1], scale_log2, -sub0));
+                float p2 = exp2f(fmaf(s[nt][2], scale_log2, -sub1));
+                float p3 = exp2f(fmaf(s[nt][3], scale_log2, -sub1));
+                l0 += p0 + p1;
+                l1 += p2 + p3;
+                pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < FA_BN / 16; kk++) {
+#pragma unroll
+                for (int dt = 0; dt < DT; dt += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    int chunk = dt + (lane >> 4);
+                    ldmatrix_x4_trans(v_s + swz<HD>(key, chunk), b0, b1, b2, b3);
+                    mma_bf16(o[dt], pf[kk], b0, b1);
+                    mma_bf16(o[dt + 1], pf[kk], b2, b3);
+                }
+            }
+        }
+        __syncthreads();   // everyone is done with this buffer before the next prefetch overwrites it
+    }
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+    const int r0 = q0 + wrow0 + g, r1 = r0 + 8;
+    __nv_bfloat16* obase = out + (long long)b * T * d + h * HD;
+#pragma unroll
+    for (int dt = 0; dt < DT; dt++) {
+        int c = dt * 8 + tq * 2;
+        if (r0 < T) *reinterpret_cast<uint32_t*>(obase + (long long)r0 * d + c) = pack_bf16(o[dt][0] * inv0, o[dt][1] * inv0);
+        if (r1 < T) *reinterpret_cast<uint32_t*>(obase + (long long)r1 * d + c) = pack_bf16(o[dt][2] * inv1, o[dt][3] * inv1);
+    }
+}
+
+// ============================================================================================ float32 kernel
+constexpr int F32_QPB = 16;     // queries per CTA (4 warps x 4 queries)
+
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;
+    u += 0x00000fffu + ((u >> 13) & 1u);
+    u &= 0xffffe000u;
+    return __uint_as_float(u);
+}
+
+template <int HD, bool CAUSAL>
+__global__ void __launch_bounds__(128)
+attention_f32_kernel(const float* __restrict__ qkv, float* __restrict__ out, int T, int H, float inv_sqrt_hd, int round_out) {
+    constexpr int DPL = HD / 32;                 // output dims per lane
+    constexpr int F32_KT = HD <= 64 ? 64 : 32;   // keys per shared-memory tile (static shared memory stays under 48 KB)
+    __shared__ float sQ[F32_QPB][HD];
+    __shared__ float sK[F32_KT][HD + 1];
+    __shared__ float sV[F32_KT][HD];
+
+    const int d = H * HD;
+    const long long row_stride = 3ll * d;
+    const int bh = blockIdx.y, b = bh / H, h = bh % H;
+    const int q0 = blockIdx.x * F32_QPB;
+    const float* qbase = qkv + (long long)b * T * row_stride + h * HD;
+    const float* kbase = qbase + d;
+    const float* vbase = qbase + 2 * d;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int i = threadIdx.x; i < F32_QPB * HD; i += 128) {
+        int r = i / HD, c = i % HD;
+        sQ[r][c] = (q0 + r < T) ? qbase[(long long)(q0 + r) * row_stride + c] : 0.f;
+    }
+    constexpr int QPW = F32_QPB / 4;
+    float m[QPW], l[QPW], o[QPW][DPL];
+#pragma unroll
+    for (int q = 0; q < QPW; q++) {
+        m[q] = -INFINITY; l[q] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o[q][i] = 0.f;
+    }
+    int kv_end = CAUSAL ? min(T, q0 + F32_QPB) : T;
+    for (int k0 = 0; k0 < kv_end; k0 += F32_KT) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < F32_KT * HD; i += 128) {
+            int r = i / HD, c = i % HD;
+            bool ok = k0 + r < T;
+            sK[r][c] = ok ? kbase[(long long)(k0 + r) * row_stride + c] : 0.f;
+            sV[r][c] = ok ? vbase[(long long)(k0 + r) * row_stride + c] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < QPW; q++) {
+            const int qi = warp * QPW + q;
+            const int qrow = q0 + qi;
+            if (qrow >= T) continue;              // uniform per warp
+#pragma unroll
+            for (int half = 0; half < F32_KT / 32; half++) {
+                const int kbeg = k0 + half * 32;
+                if (kbeg >= kv_end || (CAUSAL && kbeg > qrow)) break;     // uniform per warp
+                const int kl = half * 32 + lane;
+                const int key = k0 + kl;
+                float s = 0.f;
+#pragma unroll 8
+                for (int c = 0; c < HD; c++) s = fmaf(sQ[qi][c], sK[kl][c], s);
+                s *= inv_sqrt_hd;
+                const bool live = key < T && (!CAUSAL || key <= qrow);
+                if (!live) s = -INFINITY;
+                float mx = s;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+                const float mn = fmaxf(m[q], mx);            // finite: key `kbeg` is live for this query
+                const float alpha = expf(m[q] - mn);
+                const float p = live ? expf(s - mn) : 0.f;
+                float ps = p;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+                l[q] = l[q] * alpha + ps;
+                m[q] = mn;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[q][i] *= alpha;
+#pragma unroll 8
+                for (int jj = 0; jj < 32; jj++) {
+                    const float pj = __shfl_sync(0xffffffffu, p, jj);
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) o[q][i] = fmaf(pj, sV[half * 32 + jj][i * 32 + lane], o[q][i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < QPW; q++) {
+        const int qrow = q0 + warp * QPW + q;
+        if (qrow >= T) continue;
+        float* op = out + ((long long)b * T + qrow) * d + h * HD;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) {
+            float v = o[q][i] / l[q];
+            op[i * 32 + lane] = round_out ? round_tf32(v) : v;
+        }
+    }
+}
+
+template <int HD>
+int launch_bf16(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16* out, int B, int T, int H, int causal) {
+    const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HD * 2;
+    dim3 grid((T + FA_BM - 1) / FA_BM, B * H);
+    const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    if (causal) {
+        auto k = flash_bf16_kernel<HD, true>;
+        TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TL_LAUNCH(ctx, "attention_bf16_causal", k<<<grid, FA_THREADS, smem, ctx->stream>>>(qkv, out, T, H, scale_log2));
+    } else {
+        auto k = flash_bf16_kernel<HD, false>;
+        TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TL_LAUNCH(ctx, "attention_bf16_full", k<<<grid, FA_THREADS, smem, ctx->stream>>>(qkv, out, T, H, scale_log2));
+    }
+    return TLNN_OK;
+}
+
+template <int HD>
+int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H, int causal, int round_out) {
+    dim3 grid((T + F32_QPB - 1) / F32_QPB, B * H);
+    const float inv = 1.f / sqrtf((float)HD);
+    if (causal)
+        TL_LAUNCH(ctx, "attention_f32_causal", attention_f32_kernel<HD, true><<<grid, 128, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
+    else
+        TL_LAUNCH(ctx, "attention_f32_full", attention_f32_kernel<HD, false><<<grid, 128, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
+    return TLNN_OK;
+}
+
+}  // namespace
+
+int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int out_kind, int B, int T, int heads, int hd,
+                      int causal) {
+    if (B == 0 || T == 0) return TLNN_OK;
+    TL_REQUIRE((long long)B * heads <= 65535, "attention: batch x heads = %lld exceeds 65535", (long long)B * heads);
+    if (prec == TLNN_PREC_BF16) {
+        TL_REQUIRE(out_kind == TL_OUT_BF16, "attention: the bf16 path writes bf16");
+        const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(qkv);
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+        if (hd == 32) return launch_bf16<32>(ctx, q, o, B, T, heads, causal);
+        if (hd == 64) return launch_bf16<64>(ctx, q, o, B, T, heads, causal);
+        if (hd == 128) return launch_bf16<128>(ctx, q, o, B, T, heads, causal);
+        TL_REQUIRE(false, "attention: head dimension %d is not supported in bf16 mode (32, 64 or 128)", hd);
+    }
+    TL_REQUIRE(out_kind != TL_OUT_BF16, "attention: the float32 path writes float32");
+    const float* q = reinterpret_cast<const float*>(qkv);
+    float* o = reinterpret_cast<float*>(out);
+    const int round_out = out_kind == TL_OUT_TF32;
+    if (hd == 32) return launch_f32<32>(ctx, q, o, B, T, heads, causal, round_out);
+    if (hd == 64) return launch_f32<64>(ctx, q, o, B, T, heads, causal, round_out);
+    if (hd == 96) return launch_f32<96>(ctx, q, o, B, T, heads, causal, round_out);
+    if (hd == 128) return launch_f32<128>(ctx, q, o, B, T, heads, causal, round_out);
+    TL_REQUIRE(false, "attention: head dimension %d is not supported in float32 mode (32, 64, 96 or 128)", hd);
+}

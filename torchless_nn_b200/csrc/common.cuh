@@ -1,0 +1,158 @@
+// Shared declarations of libtlnn: context, error handling, launch bookkeeping, workspace arena.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+#include <map>
+
+#include "../../include/tlnn.h"
+
+// ---- device-side error word ------------------------------------------------------------------
+// Kernels never trap.  A kernel that meets a bad index or gives up a bounded wait records the first such
+// event here and carries on (or returns); the host reads the word at the next sync.
+struct tlnn_dev_err {
+    int code;      // 0, TLNN_ERR_INDEX or TLNN_ERR_TIMEOUT
+    int where;     // kernel-specific site id
+    long long detail;
+};
+
+__device__ __forceinline__ void tl_dev_fail(tlnn_dev_err* e, int code, int where, long long detail) {
+    if (atomicCAS(&e->code, 0, code) == 0) {
+        e->where = where;
+        e->detail = detail;
+    }
+}
+
+// ---- profiling table ----------------------------------------------------------------------------
+struct tl_prof_pending {
+    const char* name;
+    cudaEvent_t start, stop;
+};
+
+struct tlnn_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    tlnn_dev_err* d_err = nullptr;     // device memory
+    tlnn_dev_err* h_err = nullptr;     // pinned host mirror
+    long long launches = 0;
+    // grow-only scratch arena used by the composite layer calls (stream-ordered reuse)
+    char* ws = nullptr;
+    size_t ws_bytes = 0;
+    // whole-interval timing
+    cudaEvent_t prof_a = nullptr, prof_b = nullptr;
+    // per-class timing
+    bool prof_classes = false;
+    std::vector<tl_prof_pending> pending;
+    std::vector<cudaEvent_t> event_pool;
+    std::map<std::string, std::pair<long long, double>> table;
+};
+
+// ---- host-side error plumbing --------------------------------------------------------------------
+void tl_set_error(const char* fmt, ...);
+int tl_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define TL_CUDA(call)                                                             \
+    do {                                                                          \
+        cudaError_t e_ = (call);                                                  \
+        if (e_ != cudaSuccess) return tl_cuda_fail(e_, #call, __FILE__, __LINE__); \
+    } while (0)
+
+#define TL_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            tl_set_error(__VA_ARGS__);   \
+            return TLNN_ERR_VALUE;       \
+        }                                \
+    } while (0)
+
+#define TL_NOTNULL(p)                                     \
+    do {                                                  \
+        if ((p) == nullptr) {                             \
+            tl_set_error("null pointer argument: %s", #p); \
+            return TLNN_ERR_NULL;                         \
+        }                                                 \
+    } while (0)
+
+#define TL_TRY(call)              \
+    do {                          \
+        int s_ = (call);          \
+        if (s_ != TLNN_OK) return s_; \
+    } while (0)
+
+// Bracket one kernel launch: optional per-class events, launch counter, launch-error check.
+int tl_launch_begin(tlnn_ctx* ctx, const char* name);
+int tl_launch_end(tlnn_ctx* ctx, const char* name);
+
+#define TL_LAUNCH(ctx, name, ...)            \
+    do {                                     \
+        TL_TRY(tl_launch_begin(ctx, name));  \
+        __VA_ARGS__;                         \
+        TL_TRY(tl_launch_end(ctx, name));    \
+    } while (0)
+
+// ---- scratch arena ---------------------------------------------------------------------------------
+// A composite call reserves its total need up front (which may reallocate while the stream is idle), then
+// carves aligned pieces.  Pieces stay valid until the next reserve on the same context.
+int tl_ws_reserve(tlnn_ctx* ctx, size_t bytes);
+
+struct tl_ws_cursor {
+    char* base;
+    size_t off = 0;
+    explicit tl_ws_cursor(tlnn_ctx* ctx) : base(ctx->ws) {}
+    template <typename T>
+    T* take(size_t n) {
+        T* p = reinterpret_cast<T*>(base + off);
+        off += (n * sizeof(T) + 1023) & ~size_t(1023);
+        return p;
+    }
+};
+static inline size_t tl_ws_round(size_t bytes) { return (bytes + 1023) & ~size_t(1023); }
+
+// ---- internal kernels' host launchers (shared across translation units) -------------------------------
+// Output element kinds of the row kernels and the GEMM epilogue.
+enum { TL_OUT_F32 = 0, TL_OUT_BF16 = 1, TL_OUT_TF32 = 2 /* float32 storage rounded to TF32 */ };
+
+int tl_layernorm(tlnn_ctx* ctx, const float* x, const float* gamma, const float* beta, float eps,
+                 void* out, int out_kind, long long rows, int d);
+int tl_convert(tlnn_ctx* ctx, const float* x, long long ldx, void* out, int out_kind, long long rows, int cols);
+int tl_embed(tlnn_ctx* ctx, const void* ids, int ids_type, const float* table, const float* pos, float* out,
+             int B, int T, int d, int vocab);
+int tl_argmax_partials(tlnn_ctx* ctx, const float2* partials, int n_parts, int32_t* tokens, long long rows);
+
+// Epilogue description of the tensor-core GEMM: out = act(acc + bias) + residual, with optional row remapping
+// (used by the ViT projector to drop patch rows behind the class token) and optional per-tile arg-max.
+struct tl_gemm_epilogue {
+    const float* bias = nullptr;        // (N) or null
+    int act = TLNN_ACT_NONE;
+    const float* residual = nullptr;    // float32, pitch ldr, or null
+    long long ldr = 0;
+    int res_row_mod = 0;                // >0: residual row = res_row_off + row % res_row_mod
+    int res_row_off = 0;
+    void* out = nullptr;                // may be null when only argmax partials are wanted
+    long long ldo = 0;
+    int out_kind = TL_OUT_F32;
+    int row_group = 0;                  // >0: out row = (row / row_group) * out_group + out_off + row % row_group
+    int out_group = 0;
+    int out_off = 0;
+    float2* argmax_partials = nullptr;  // (M, n_tiles) of (max, index as float bits) or null
+    int accurate_math = 0;              // 1: libm-grade tanh in the activation, 0: hardware approximation
+};
+
+// A (M,K) and W (N,K) both with the contraction dimension contiguous, of element kind `prec`
+// (TLNN_PREC_BF16: __nv_bfloat16, TLNN_PREC_TF32: float).  lda / ldw in elements.
+int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w, long long ldw,
+            int M, int N, int K, const tl_gemm_epilogue& ep);
+// Tile width the GEMM will pick for this problem; the arg-max partial buffer has ceil(N / width) entries per row.
+int tl_gemm_bn(int M, int N, int sm_count);
+
+// Fused attention on a packed projection buffer: qkv is (B, T, 3d) with columns [0,d) Q, [d,2d) K, [2d,3d) V
+// and head h at columns h*hd..(h+1)*hd inside each third.  out is (B, T, d) of the same kind.
+int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int out_kind,
+                      int B, int T, int heads, int hd, int causal);

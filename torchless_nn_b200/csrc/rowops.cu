@@ -1,0 +1,527 @@
+// Bandwidth-bound kernels: embedding gather, LayerNorm, softmax, arg-max, type conversion, weight re-layout,
+// patch extraction and the small element-wise helpers.  All use 128-bit loads/stores where the row width
+// and the pointers allow it and fall back to scalar accesses otherwise.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarp = 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Round a float32 to the nearest TF32 value (10-bit mantissa, ties to even), result kept in float32 storage.
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;   // inf / nan unchanged
+    u += 0x00000fffu + ((u >> 13) & 1u);
+    u &= 0xffffe000u;
+    return __uint_as_float(u);
+}
+
+template <int KIND>
+__device__ __forceinline__ void store4(void* out, long long idx, float4 v) {
+    if constexpr (KIND == TL_OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + idx) = v;
+    } else if constexpr (KIND == TL_OUT_TF32) {
+        float4 r = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + idx) = r;
+    } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y);
+        __nv_bfloat162 b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 p;
+        p.x = *reinterpret_cast<uint32_t*>(&a);
+        p.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + idx) = p;
+    }
+}
+template <int KIND>
+__device__ __forceinline__ void store1(void* out, long long idx, float v) {
+    if constexpr (KIND == TL_OUT_F32) reinterpret_cast<float*>(out)[idx] = v;
+    else if constexpr (KIND == TL_OUT_TF32) reinterpret_cast<float*>(out)[idx] = round_tf32(v);
+    else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+}
+
+// ---- embedding gather -------------------------------------------------------------------------------
+// One warp per token row: out[row,:] = table[id,:] + pos[t,:].  The single float add is exact, so the result
+// is bit-identical to the NumPy path.
+template <bool VEC>
+__global__ void embed_kernel(const void* __restrict__ ids, int ids_type, const float* __restrict__ table,
+                             const float* __restrict__ pos, float* __restrict__ out, long long rows, int T, int d,
+                             int vocab, tlnn_dev_err* err) {
+    long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
+    int lane = threadIdx.x % kWarp;
+    if (row >= rows) return;
+    long long id;
+    if (ids_type == TLNN_I32) id = reinterpret_cast<const int32_t*>(ids)[row];
+    else if (ids_type == TLNN_I64) id = reinterpret_cast<const int64_t*>(ids)[row];
+    else id = reinterpret_cast<const uint8_t*>(ids)[row];
+    if (id < 0) id += vocab;
+    if (id < 0 || id >= vocab) {
+        if (lane == 0) tl_dev_fail(err, TLNN_ERR_INDEX, 1, id < 0 ? id - vocab : id);
+        id = 0;
+    }
+    int t = (int)(row % T);
+    const float* src = table + id * d;
+    const float* p = pos + (long long)t * d;
+    float* dst = out + row * d;
+    if constexpr (VEC) {
+        for (int c = lane * 4; c < d; c += kWarp * 4) {
+            float4 a = __ldg(reinterpret_cast<const float4*>(src + c));
+            float4 b = __ldg(reinterpret_cast<const float4*>(p + c));
+            float4 r = make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+            *reinterpret_cast<float4*>(dst + c) = r;
+        }
+    } else {
+        for (int c = lane; c < d; c += kWarp) dst[c] = __fadd_rn(src[c], p[c]);
+    }
+}
+
+// ---- LayerNorm -----------------------------------------------------------------------------------------
+// One warp per row, the row held in registers (up to 32 x float4 per lane, d <= 4096): mean, then the mean of
+// squared deviations (the two-pass form NumPy's var uses), then (x - mean) / sqrt(var + eps) * gamma + beta.
+template <int KIND, int VPL /* float4 per lane */>
+__global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                      const float* __restrict__ beta, float eps, void* __restrict__ out,
+                                      long long rows, int d) {
+    long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
+    int lane = threadIdx.x % kWarp;
+    if (row >= rows) return;
+    const float4* src = reinterpret_cast<const float4*>(x + row * d);
+    int nvec = d / 4;
+    float4 v[VPL];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+        int c = i * kWarp + lane;
+        if (c < nvec) {
+            v[i] = src[c];
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float mean = warp_sum(s) / (float)d;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+        int c = i * kWarp + lane;
+        if (c < nvec) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+    }
+    float var = warp_sum(q) / (float)d;
+    float stdv = sqrtf(var + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+        int c = i * kWarp + lane;
+        if (c < nvec) {
+            float4 g = __ldg(g4 + c), b = __ldg(b4 + c);
+            float4 r;
+            r.x = g.x * (v[i].x / stdv) + b.x;
+            r.y = g.y * (v[i].y / stdv) + b.y;
+            r.z = g.z * (v[i].z / stdv) + b.z;
+            r.w = g.w * (v[i].w / stdv) + b.w;
+            store4<KIND>(out, row * d + c * 4, r);
+        }
+    }
+}
+
+// Any width: one block per row, three passes over the row (second and third hit L1/L2).
+template <int KIND>
+__global__ void layernorm_block_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                       const float* __restrict__ beta, float eps, void* __restrict__ out,
+                                       long long rows, int d) {
+    __shared__ float red[32];
+    __shared__ float bcast;
+    long long row = blockIdx.x;
+    const float* src = x + row * d;
+    int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarp = blockDim.x / kWarp;
+    auto block_sum = [&](float v) {
+        v = warp_sum(v);
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            float t = lane < nwarp ? red[lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) bcast = t;
+        }
+        __syncthreads();
+        float r = bcast;
+        __syncthreads();
+        return r;
+    };
+    float s = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) s += src[c];
+    float mean = block_sum(s) / (float)d;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { float t = src[c] - mean; q += t * t; }
+    float var = block_sum(q) / (float)d;
+    float stdv = sqrtf(var + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x)
+        store1<KIND>(out, row * d + c, gamma[c] * ((src[c] - mean) / stdv) + beta[c]);
+}
+
+// ---- strided float32 -> {bf16, tf32-rounded, f32} copy -------------------------------------------------
+template <int KIND>
+__global__ void convert_kernel(const float* __restrict__ x, long long ldx, void* __restrict__ out, long long rows,
+                               int cols, bool vec) {
+    long long total4 = rows * (long long)(cols / 4);
+    long long stride = (long long)gridDim.x * blockDim.x;
+    long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec) {
+        int c4 = cols / 4;
+        for (long long i = i0; i < total4; i += stride) {
+            long long r = i / c4;
+            int c = (int)(i % c4) * 4;
+            float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
+            store4<KIND>(out, r * cols + c, v);
+        }
+    } else {
+        long long total = rows * (long long)cols;
+        for (long long i = i0; i < total; i += stride) {
+            long long r = i / cols;
+            int c = (int)(i % cols);
+            store1<KIND>(out, i, x[r * ldx + c]);
+        }
+    }
+}
+
+// ---- weight transpose + convert: (rows, cols) float32 -> (cols, rows) of KIND --------------------------------
+template <int KIND>
+__global__ void transpose_convert_kernel(const float* __restrict__ w, int rows, int cols, void* __restrict__ out) {
+    __shared__ float tile[32][33];
+    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        int r = r0 + j, c = c0 + threadIdx.x;
+        tile[j][threadIdx.x] = (r < rows && c < cols) ? w[(long long)r * cols + c] : 0.f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        int c = c0 + j, r = r0 + threadIdx.x;
+        if (c < cols && r < rows) store1<KIND>(out, (long long)c * rows + r, tile[threadIdx.x][j]);
+    }
+}
+
+// ---- softmax with temperature ----------------------------------------------------------------------------
+// One block per row.  Pass 1 finds the maximum, pass 2 the sum of exp((x - max) / T), pass 3 writes; the row
+// (up to ~200 KB) stays in L2 between the passes, so DRAM sees one read and one write.
+__global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ out, int cols, float temperature) {
+    __shared__ float red[32];
+    __shared__ float bcast;
+    const float* src = x + (long long)blockIdx.x * cols;
+    float* dst = out + (long long)blockIdx.x * cols;
+    int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarp = blockDim.x / kWarp;
+    float m = -INFINITY;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, src[c]);
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    m = bcast;
+    __syncthreads();
+    float s = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) s += expf((src[c] - m) / temperature);
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    s = bcast;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = expf((src[c] - m) / temperature) / s;
+}
+
+// ---- arg-max ---------------------------------------------------------------------------------------------
+// First index of the maximum, as numpy.argmax.  NaN handling: NumPy returns the first NaN; logits here are
+// finite, and a NaN row yields the first maximum among the comparable values.
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__global__ void argmax_kernel(const float* __restrict__ x, long long ldx, int32_t* __restrict__ out, int cols) {
+    __shared__ float rv[32];
+    __shared__ int ri[32];
+    const float* src = x + (long long)blockIdx.x * ldx;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) argmax_combine(v, idx, src[c], c);
+    int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarp = blockDim.x / kWarp;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_combine(v, idx, ov, oi);
+    }
+    if (lane == 0) { rv[warp] = v; ri[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < nwarp ? rv[lane] : -INFINITY;
+        idx = lane < nwarp ? ri[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            argmax_combine(v, idx, ov, oi);
+        }
+        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+// Reduce the per-tile (max, index) pairs a GEMM epilogue left behind: one warp per row.
+__global__ void argmax_partials_kernel(const float2* __restrict__ parts, int n_parts, int32_t* __restrict__ out,
+                                       long long rows) {
+    long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
+    int lane = threadIdx.x % kWarp;
+    if (row >= rows) return;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int p = lane; p < n_parts; p += kWarp) {
+        float2 e = parts[row * n_parts + p];
+        argmax_combine(v, idx, e.x, __float_as_int(e.y));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_combine(v, idx, ov, oi);
+    }
+    if (lane == 0) out[row] = idx == 0x7fffffff ? 0 : idx;
+}
+
+// ---- element-wise helpers -----------------------------------------------------------------------------------
+__global__ void axpby_kernel(float* __restrict__ x, float alpha, const float* __restrict__ y, float beta, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = alpha == 0.f ? 0.f : x[i] * alpha;    // alpha 0 is "fill": do not propagate old NaNs
+        if (y) v += beta * y[i];
+        else v += beta;
+        x[i] = v;
+    }
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = a[i] + b[i];
+}
+
+__global__ void gather_kernel(const float* __restrict__ src, const int64_t* __restrict__ index,
+                              float* __restrict__ dst, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = src[index[i]];
+}
+
+__global__ void activation_kernel(int act, const float* __restrict__ x, float* __restrict__ out, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = x[i], r;
+        if (act == TLNN_ACT_GELU) {
+            float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+            r = 0.5f * v * (1.f + tanhf(u));
+        } else if (act == TLNN_ACT_SILU) {
+            r = v * ((1.f + tanhf(v * 0.5f)) * 0.5f);
+        } else if (act == TLNN_ACT_RELU) {
+            r = fmaxf(v, 0.f);
+        } else {
+            r = v;
+        }
+        out[i] = r;
+    }
+}
+
+int grid_for(size_t n, int block, int sm_count) {
+    size_t g = (n + block - 1) / block;
+    size_t cap = (size_t)sm_count * 16;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// ---- host launchers ---------------------------------------------------------------------------------------------
+int tl_embed(tlnn_ctx* ctx, const void* ids, int ids_type, const float* table, const float* pos, float* out,
+             int B, int T, int d, int vocab) {
+    long long rows = (long long)B * T;
+    if (rows == 0) return TLNN_OK;
+    const int warps = 8;
+    unsigned grid = (unsigned)((rows + warps - 1) / warps);
+    bool vec = (d % 4 == 0) && aligned16(table) && aligned16(pos) && aligned16(out);
+    if (vec)
+        TL_LAUNCH(ctx, "embed_gather", embed_kernel<true><<<grid, warps * 32, 0, ctx->stream>>>(
+                      ids, ids_type, table, pos, out, rows, T, d, vocab, ctx->d_err));
+    else
+        TL_LAUNCH(ctx, "embed_gather", embed_kernel<false><<<grid, warps * 32, 0, ctx->stream>>>(
+                      ids, ids_type, table, pos, out, rows, T, d, vocab, ctx->d_err));
+    return TLNN_OK;
+}
+
+template <int KIND>
+static int layernorm_dispatch(tlnn_ctx* ctx, const float* x, const float* gamma, const float* beta, float eps,
+                              void* out, long long rows, int d) {
+    bool vec = (d % 4 == 0) && d <= 4096 && aligned16(x) && aligned16(gamma) && aligned16(beta) && aligned16(out);
+    if (vec) {
+        const int warps = 4;
+        unsigned grid = (unsigned)((rows + warps - 1) / warps);
+        int vpl = (d / 4 + 31) / 32;
+#define LN_CASE(V)                                                                                              \
+    TL_LAUNCH(ctx, "layernorm", layernorm_warp_kernel<KIND, V><<<grid, warps * 32, 0, ctx->stream>>>(          \
+                  x, gamma, beta, eps, out, rows, d))
+        if (vpl <= 1) LN_CASE(1);
+        else if (vpl <= 2) LN_CASE(2);
+        else if (vpl <= 4) LN_CASE(4);
+        else if (vpl <= 6) LN_CASE(6);
+        else if (vpl <= 8) LN_CASE(8);
+        else if (vpl <= 16) LN_CASE(16);
+        else LN_CASE(32);
+#undef LN_CASE
+    } else {
+        TL_LAUNCH(ctx, "layernorm", layernorm_block_kernel<KIND><<<(unsigned)rows, 256, 0, ctx->stream>>>(
+                      x, gamma, beta, eps, out, rows, d));
+    }
+    return TLNN_OK;
+}
+
+int tl_layernorm(tlnn_ctx* ctx, const float* x, const float* gamma, const float* beta, float eps, void* out,
+                 int out_kind, long long rows, int d) {
+    if (rows == 0) return TLNN_OK;
+    TL_REQUIRE(rows < (1ll << 31), "too many rows");
+    if (out_kind == TL_OUT_F32) return layernorm_dispatch<TL_OUT_F32>(ctx, x, gamma, beta, eps, out, rows, d);
+    if (out_kind == TL_OUT_BF16) return layernorm_dispatch<TL_OUT_BF16>(ctx, x, gamma, beta, eps, out, rows, d);
+    return layernorm_dispatch<TL_OUT_TF32>(ctx, x, gamma, beta, eps, out, rows, d);
+}
+
+int tl_convert(tlnn_ctx* ctx, const float* x, long long ldx, void* out, int out_kind, long long rows, int cols) {
+    if (rows == 0 || cols == 0) return TLNN_OK;
+    bool vec = (cols % 4 == 0) && (ldx % 4 == 0) && aligned16(x) && aligned16(out);
+    size_t n = (size_t)rows * cols / (vec ? 4 : 1);
+    int grid = grid_for(n, 256, ctx->sm_count);
+    if (out_kind == TL_OUT_BF16)
+        TL_LAUNCH(ctx, "convert", convert_kernel<TL_OUT_BF16><<<grid, 256, 0, ctx->stream>>>(x, ldx, out, rows, cols, vec));
+    else if (out_kind == TL_OUT_TF32)
+        TL_LAUNCH(ctx, "convert", convert_kernel<TL_OUT_TF32><<<grid, 256, 0, ctx->stream>>>(x, ldx, out, rows, cols, vec));
+    else
+        TL_LAUNCH(ctx, "convert", convert_kernel<TL_OUT_F32><<<grid, 256, 0, ctx->stream>>>(x, ldx, out, rows, cols, vec));
+    return TLNN_OK;
+}
+
+int tl_argmax_partials(tlnn_ctx* ctx, const float2* partials, int n_parts, int32_t* tokens, long long rows) {
+    if (rows == 0) return TLNN_OK;
+    const int warps = 8;
+    unsigned grid = (unsigned)((rows + warps - 1) / warps);
+    TL_LAUNCH(ctx, "argmax_partials",
+              argmax_partials_kernel<<<grid, warps * 32, 0, ctx->stream>>>(partials, n_parts, tokens, rows));
+    return TLNN_OK;
+}
+
+// ---- C ABI ---------------------------------------------------------------------------------------------------------
+extern "C" int tlnn_embed_fwd(tlnn_ctx* ctx, const void* ids, int ids_type, const float* table, const float* pos,
+                              float* out, int B, int T, int d, int vocab) {
+    TL_NOTNULL(ctx); TL_NOTNULL(ids); TL_NOTNULL(table); TL_NOTNULL(pos); TL_NOTNULL(out);
+    TL_REQUIRE(B >= 0 && T >= 0 && d > 0 && vocab > 0, "embed: bad shape B=%d T=%d d=%d vocab=%d", B, T, d, vocab);
+    TL_REQUIRE(ids_type == TLNN_I32 || ids_type == TLNN_I64 || ids_type == TLNN_U8,
+               "embed: token ids must be int32, int64 or uint8");
+    TL_CUDA(cudaSetDevice(ctx->device));
+    return tl_embed(ctx, ids, ids_type, table, pos, out, B, T, d, vocab);
+}
+
+extern "C" int tlnn_layernorm_fwd(tlnn_ctx* ctx, const float* x, const float* gamma, const float* beta, float eps,
+                                  float* out, long long rows, int d) {
+    TL_NOTNULL(ctx); TL_NOTNULL(x); TL_NOTNULL(gamma); TL_NOTNULL(beta); TL_NOTNULL(out);
+    TL_REQUIRE(rows >= 0 && d > 0, "layernorm: bad shape rows=%lld d=%d", rows, d);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    return tl_layernorm(ctx, x, gamma, beta, eps, out, TL_OUT_F32, rows, d);
+}
+
+extern "C" int tlnn_activation_fwd(tlnn_ctx* ctx, int act, const float* x, float* out, size_t n) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(act >= TLNN_ACT_NONE && act <= TLNN_ACT_RELU, "unknown activation %d", act);
+    if (n == 0) return TLNN_OK;
+    TL_NOTNULL(x); TL_NOTNULL(out);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "activation", activation_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(act, x, out, n));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long long rows, int cols, float temperature) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31), "softmax: bad shape rows=%lld cols=%d", rows, cols);
+    if (rows == 0) return TLNN_OK;
+    TL_NOTNULL(x); TL_NOTNULL(out);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    int block = cols >= 8192 ? 1024 : (cols >= 1024 ? 256 : 64);
+    TL_LAUNCH(ctx, "softmax", softmax_kernel<<<(unsigned)rows, block, 0, ctx->stream>>>(x, out, cols, temperature));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_argmax_fwd(tlnn_ctx* ctx, const float* x, long long ldx, int32_t* out, long long rows, int cols) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31) && ldx >= cols, "argmax: bad shape rows=%lld cols=%d", rows, cols);
+    if (rows == 0) return TLNN_OK;
+    TL_NOTNULL(x); TL_NOTNULL(out);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    int block = cols >= 8192 ? 1024 : (cols >= 1024 ? 256 : 64);
+    TL_LAUNCH(ctx, "argmax", argmax_kernel<<<(unsigned)rows, block, 0, ctx->stream>>>(x, ldx, out, cols));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_axpby_f32(tlnn_ctx* ctx, float* x, float alpha, const float* y, float beta, size_t n) {
+    TL_NOTNULL(ctx);
+    if (n == 0) return TLNN_OK;
+    TL_NOTNULL(x);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "axpby", axpby_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, alpha, y, beta, n));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_add_f32(tlnn_ctx* ctx, const float* a, const float* b, float* out, size_t n) {
+    TL_NOTNULL(ctx);
+    if (n == 0) return TLNN_OK;
+    TL_NOTNULL(a); TL_NOTNULL(b); TL_NOTNULL(out);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "add", add_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(a, b, out, n));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_gather_f32(tlnn_ctx* ctx, const float* src, const int64_t* index, float* dst, size_t n) {
+    TL_NOTNULL(ctx);
+    if (n == 0) return TLNN_OK;
+    TL_NOTNULL(src); TL_NOTNULL(index); TL_NOTNULL(dst);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "gather", gather_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(src, index, dst, n));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_weight_prepare(tlnn_ctx* ctx, const float* w, int rows, int cols, int transpose, int prec, void* out) {
+    TL_NOTNULL(ctx); TL_NOTNULL(w); TL_NOTNULL(out);
+    TL_REQUIRE(rows > 0 && cols > 0, "weight_prepare: bad shape %d x %d", rows, cols);
+    TL_REQUIRE(prec == TLNN_PREC_TF32 || prec == TLNN_PREC_BF16, "weight_prepare: unknown precision %d", prec);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    int kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_TF32;
+    if (!transpose) return tl_convert(ctx, w, cols, out, kind, rows, cols);
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+    if (kind == TL_OUT_BF16)
+        TL_LAUNCH(ctx, "weight_transpose", transpose_convert_kernel<TL_OUT_BF16><<<grid, block, 0, ctx->stream>>>(w, rows, cols, out));
+    else
+        TL_LAUNCH(ctx, "weight_transpose", transpose_convert_kernel<TL_OUT_TF32><<<grid, block, 0, ctx->stream>>>(w, rows, cols, out));
+    return TLNN_OK;
+}
