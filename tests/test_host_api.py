@@ -1,0 +1,106 @@
+"""CPU tests of the boundary: the shared library loads, exports every symbol the header declares, validates its
+arguments on the host before touching a device, and fails loudly without a GPU."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "tlnn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tlnn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from torchless_nn_b200 import _lib
+    names = _declared()
+    assert len(names) >= 40
+    for n in names:
+        assert hasattr(_lib.lib, n), f"{n} is declared in tlnn.h but not exported"
+        assert n in _lib.PROTOTYPES, f"{n} has no ctypes prototype"
+    assert sorted(_lib.PROTOTYPES) == names
+    assert _lib.lib.tlnn_version() >= 100
+
+
+def test_status_codes_map_to_reference_exception_classes():
+    from torchless_nn_b200 import _lib
+    for code, exc in ((_lib.ERR_VALUE, ValueError), (_lib.ERR_INDEX, IndexError), (_lib.ERR_CUDA, RuntimeError),
+                      (_lib.ERR_NOMEM, MemoryError), (_lib.ERR_TIMEOUT, RuntimeError), (_lib.ERR_NULL, ValueError)):
+        with pytest.raises(exc):
+            _lib.check(code)
+    _lib.check(_lib.OK)
+
+
+def test_null_and_bad_arguments_are_rejected_on_the_host():
+    from torchless_nn_b200 import _lib
+    lib = _lib.lib
+    assert lib.tlnn_init(0, None) == _lib.ERR_NULL
+    assert lib.tlnn_sync(None) == _lib.ERR_NULL
+    assert lib.tlnn_layernorm_fwd(None, None, None, None, 1e-5, None, 1, 8) == _lib.ERR_NULL
+    assert lib.tlnn_gpt_prefill(None, None, None, 2, 1, 1, None, None) == _lib.ERR_NULL
+    assert b"null" in lib.tlnn_last_error()
+    assert lib.tlnn_launch_count(None, 0) == 0
+    assert lib.tlnn_decode_end(None) in (_lib.OK, _lib.ERR_NULL)
+
+
+def test_no_gpu_means_an_error_not_a_fallback():
+    """On a machine without a GPU the engine refuses to start; nothing computes on the CPU."""
+    from torchless_nn_b200 import _lib
+    h = C.c_void_p()
+    status = _lib.lib.tlnn_init(0, C.byref(h))
+    if status == _lib.OK:
+        _lib.lib.tlnn_shutdown(h)
+        pytest.skip("a GPU is present")
+    assert status == _lib.ERR_CUDA
+    with pytest.raises(RuntimeError):
+        _lib.check(status)
+
+
+def test_backend_rejects_other_runtimes(monkeypatch):
+    import importlib
+    import torchless_nn_b200.backend as be
+    monkeypatch.setenv("XP_RUNTIME", "CPU")
+    with pytest.raises(AssertionError):
+        importlib.reload(be)
+    monkeypatch.setenv("XP_RUNTIME", "B200")
+    importlib.reload(be)
+    assert be.runtime == "B200" and be.FLOAT_TYPE is np.float32
+    with pytest.raises(ValueError):
+        be.set_precision("fp8")
+
+
+def test_mirror_modules_export_the_reference_names():
+    from torchless_nn_b200 import layers, activations, transformer_adapters, network, utils, backend
+    for mod, names in ((layers, ["Dense", "Dropout", "MultiHeadAttention", "TransformerFeedForward", "LayerNorm",
+                                 "TransformerBlock"]),
+                       (activations, ["ReLU", "GeLU", "SiLU", "SoftMax"]),
+                       (transformer_adapters, ["VitProjector", "VitMLPHead", "GPTEmbeddingTable", "GPTEmbedFront",
+                                               "GPTEmbedBack"]),
+                       (network, ["Network"]), (utils, ["Layer", "Residual"]),
+                       (backend, ["xp", "FLOAT_TYPE", "runtime", "init_random_tensor", "init_zeros_tensor"])):
+        for n in names:
+            assert hasattr(mod, n), (mod.__name__, n)
+    import inspect
+    sig = inspect.signature(layers.TransformerBlock.__init__)
+    assert list(sig.parameters)[1:] == ["embed_dim", "context_length", "num_heads", "activation", "decoder",
+                                        "attn_dropout_rate", "res_dropout_rate"]
+    sig = inspect.signature(layers.MultiHeadAttention.__init__)
+    assert list(sig.parameters)[1:] == ["embedding_dim", "context_length", "num_heads", "decoder",
+                                        "attn_dropout_rate", "res_dropout_rate"]
+    sig = inspect.signature(transformer_adapters.VitProjector.__init__)
+    assert list(sig.parameters)[1:] == ["input_size", "patch_size", "embedding_dim", "num_registers"]
+
+
+def test_product_code_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "torchless_nn_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f"{f} imports the oracle"
+                assert "oracle/" not in text and "oracle." not in text, f"{f} reaches into the oracle"
