@@ -155,6 +155,23 @@ int tlnn_norm_logits_fwd(tlnn_ctx* ctx, int prec, const float* x, const float* g
                          const void* table_t, const float* bias, float* logits, int32_t* tokens,
                          long long rows, int d, int vocab);
 
+/* Arg-max head for callers that must not allocate.  No counterpart in the reference: it computes what
+ * tlnn_logits_fwd(ctx, prec, x, table_t, bias, NULL, tokens, rows, d, vocab) computes, but takes its intermediates
+ * (the converted operand rows and the per-tile arg-max candidates) from a TLNN_NOALLOC_SCRATCH_BYTES array built into
+ * the library image, so the call never reaches cudaMalloc, cudaFree, the context's scratch arena or any other
+ * allocating routine.  It is meant for hosts where allocation is off the table at call time: a serving process whose
+ * own memory manager has claimed the whole GPU up front and hands out sub-buffers (x and tokens come from there), or a
+ * latency-critical loop that cannot afford the device-wide stall an allocation may cause.
+ *  - Every GPU that loads libtlnn.so keeps the array resident until the process exits.
+ *  - Shapes whose intermediates exceed the array are refused with TLNN_ERR_VALUE and a message that states the need.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that call during
+ *    set-up, before any stream capture begins.
+ *  - All calls on a device share the one array and leave their data in it; nothing in it has to be zero on entry.
+ *    Two calls whose kernels can overlap on the GPU (different contexts/streams on one device) race: serialise them. */
+#define TLNN_NOALLOC_SCRATCH_BYTES (16u << 20)
+int tlnn_logits_tokens_noalloc(tlnn_ctx* ctx, int prec, const float* x, const void* table_t, const float* bias,
+                               int32_t* tokens, long long rows, int d, int vocab);
+
 /* VitProjector.forward (transformer_adapters.py:34-55).  img (B, C, H, W) float32; proj_t prepared
  * (d, ph*pw*C); cls_reg (1+regs, d); pos (1+regs+N, d); out (B, 1+regs+N, d). */
 int tlnn_vit_project_fwd(tlnn_ctx* ctx, int prec, const float* img, const void* proj_t, const float* cls_reg,

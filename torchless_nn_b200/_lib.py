@@ -75,6 +75,7 @@ PROTOTYPES = {
                                  C.c_int, C.c_int]),
     "tlnn_logits_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, ll, C.c_int, C.c_int]),
     "tlnn_norm_logits_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, ll, C.c_int, C.c_int]),
+    "tlnn_logits_tokens_noalloc": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, ll, C.c_int, C.c_int]),
     "tlnn_vit_project_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp] + [C.c_int] * 8),
     "tlnn_vit_head_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tlnn_gpt_prefill": (C.c_int, [vp, C.POINTER(GPTModel), vp, C.c_int, C.c_int, C.c_int, vp, vp]),
