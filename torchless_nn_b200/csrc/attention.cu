@@ -71,7 +71,7 @@ __device__ __forceinline__ void load_tile(uint8_t* dst_base, const __nv_bfloat16
 }
 
 template <int HD, bool CAUSAL>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, HD <= 64 ? 2 : 1)
 flash_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, int T, int H, float scale_log2) {
     constexpr int KSTEPS = HD / 16;       // k-steps of the S = Q K^T product
     constexpr int DT = HD / 8;            // 8-wide output column tiles
@@ -340,10 +340,12 @@ int launch_bf16(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16* out, int
     if (causal) {
         auto k = flash_bf16_kernel<HD, true>;
         TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         TL_LAUNCH(ctx, "attention_bf16_causal", k<<<grid, FA_THREADS, smem, ctx->stream>>>(qkv, out, T, H, scale_log2));
     } else {
         auto k = flash_bf16_kernel<HD, false>;
         TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         TL_LAUNCH(ctx, "attention_bf16_full", k<<<grid, FA_THREADS, smem, ctx->stream>>>(qkv, out, T, H, scale_log2));
     }
     return TLNN_OK;

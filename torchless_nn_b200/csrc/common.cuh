@@ -141,7 +141,7 @@ struct tl_gemm_epilogue {
     int row_group = 0;                  // >0: out row = (row / row_group) * out_group + out_off + row % row_group
     int out_group = 0;
     int out_off = 0;
-    float2* argmax_partials = nullptr;  // (M, n_tiles) of (max, index as float bits) or null
+    float2* argmax_partials = nullptr;  // (M, tl_gemm_argmax_parts) of (max, index as float bits) or null
     int accurate_math = 0;              // 1: libm-grade tanh in the activation, 0: hardware approximation
 };
 
@@ -149,8 +149,10 @@ struct tl_gemm_epilogue {
 // (TLNN_PREC_BF16: __nv_bfloat16, TLNN_PREC_TF32: float).  lda / ldw in elements.
 int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w, long long ldw,
             int M, int N, int K, const tl_gemm_epilogue& ep);
-// Tile width the GEMM will pick for this problem; the arg-max partial buffer has ceil(N / width) entries per row.
+// Tile width the GEMM will pick for this problem, and the number of arg-max candidates it leaves per row
+// (the partial buffer holds rows x tl_gemm_argmax_parts float2 entries).
 int tl_gemm_bn(int M, int N, int sm_count);
+int tl_gemm_argmax_parts(int M, int N, int sm_count);
 
 // Fused attention on a packed projection buffer: qkv is (B, T, 3d) with columns [0,d) Q, [d,2d) K, [2d,3d) V
 // and head h at columns h*hd..(h+1)*hd inside each third.  out is (B, T, d) of the same kind.

@@ -7,9 +7,11 @@
 //                 operands) from shared memory into one of two TMEM accumulators (BN columns each), frees each stage
 //                 with tcgen05.commit -> `empty[stage]`, and hands a finished accumulator over with
 //                 tcgen05.commit -> `acc_full[buf]`;
-//   warps 2..5  - epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes of its warp-id mod 4),
-//                 apply bias / activation / residual / arg-max, store, then release the accumulator
-//                 (`acc_empty[buf]`) so that the next tile's MMAs overlap this tile's epilogue.
+//   warps 2..9  - epilogue: tcgen05.ld the accumulator (a warp may read the 32 TMEM lanes of its warp-id mod 4; two
+//                 warps share a row quarter and split its columns), apply bias / activation / arg-max, transpose
+//                 through shared memory, add the residual and store whole 128-byte row segments; the accumulator is
+//                 released (`acc_empty[buf]`) as soon as its last chunk is in registers, so the next tile's MMAs
+//                 overlap this tile's epilogue.
 // Every wait on an mbarrier is bounded by wall-clock time; on expiry the kernel records TLNN_ERR_TIMEOUT in the
 // context's error word, raises a CTA-wide abort flag, and all roles fall through to the common exit, where the
 // TMEM allocation is returned.
@@ -23,7 +25,7 @@ constexpr int BM = 128;             // UMMA M (cta_group::1)
 constexpr int ROW_BYTES = 128;      // one swizzle-128B row of K: 64 bf16 or 32 float32
 constexpr int MMA_K_BYTES = 32;     // K extent of one tcgen05.mma: 16 bf16 or 8 tf32
 constexpr int GROUP_M = 8;          // rasterisation: tiles are walked in groups of GROUP_M row-blocks
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, eight epilogue warps
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 template <int BN> struct Cfg {
@@ -32,7 +34,9 @@ template <int BN> struct Cfg {
     static constexpr uint32_t B_BYTES = BN * ROW_BYTES;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr uint32_t BAR_BYTES = 256;
+    static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;     // eight 4 KB staging tiles
+    static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024 /*alignment slack*/;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------------------------
@@ -122,8 +126,9 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-    uint32_t r[32];
+// The load is split in two: request the chunk, and later wait for every outstanding request of this thread.  The
+// destination registers must not be read between the two.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -134,10 +139,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes
 // apart (stride byte offset), descriptor version 1 (sm_100).
@@ -187,6 +190,36 @@ __device__ __forceinline__ float apply_act(int act, float v) {
     return v;
 }
 
+// Activation over a 32-element chunk with the selector hoisted out of the element loop, so that the 32 independent
+// chains are scheduled together.
+template <bool ACCURATE>
+__device__ __forceinline__ void apply_act_chunk(int act, float (&v)[32]) {
+    if (act == TLNN_ACT_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float x = v[j];
+            if (ACCURATE) {
+                const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+                v[j] = 0.5f * x * (1.f + tanhf(u));
+            } else {
+                const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
+                const float h = 0.5f * x;
+                v[j] = fmaf(h, tanh_fast(u), h);
+            }
+        }
+    } else if (act == TLNN_ACT_SILU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float x = v[j];
+            const float t = ACCURATE ? tanhf(0.5f * x) : tanh_fast(0.5f * x);
+            v[j] = x * ((1.f + t) * 0.5f);
+        }
+    } else if (act == TLNN_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+    }
+}
+
 struct TileCoord { int m_blk, n_blk; };
 __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles) {
     int per_group = GROUP_M * n_tiles;
@@ -200,8 +233,199 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles)
     return c;
 }
 
+// ---- epilogue -------------------------------------------------------------------------------------------------------------
+// Epilogue variants.  The specialised ones carry only the code of one fused pattern, which keeps the instruction
+// footprint of the eight epilogue warps small (the generic variant with every option compiled in runs out of
+// instruction cache); the host picks a specialised variant only when its alignment and shape conditions hold.
+enum {
+    EPI_GENERIC = 0,     // everything decided at run time; any alignment, ragged N, row remapping
+    EPI_BF16 = 1,        // bf16 out (+bias)                         N % 32 == 0, 16-byte aligned rows
+    EPI_BF16_GELU = 2,   // bf16 out, bias, tanh-GeLU (hardware tanh)  same conditions
+    EPI_F32_RES = 3,     // float32 out (+bias) + float32 residual     same conditions, residual rows aligned too
+    EPI_ARGMAX = 4       // no output, (+bias), per-row arg-max candidates; ragged N allowed
+};
+
+// Two warps share each 32-row quarter of the tile (a warp may only read the TMEM lanes of its warp-id mod 4) and take
+// the even / odd 32-column chunks.  Per chunk:
+//   phase 1 (thread = row): accumulator chunk from TMEM, + bias, activation, arg-max, then into this warp's 32 x 32
+//                           float staging tile in shared memory (16-byte units XOR-swizzled by row);
+//   phase 2 (8 lanes = one 128-byte row segment): read the tile transposed, + residual, convert, store - every store
+//                           instruction writes four whole row segments.
+// The bias and the residual of a chunk are requested before its accumulator is waited for, and the accumulator
+// buffer goes back to the MMA warp as soon as this warp's last chunk is in registers.
+template <int BN, int MODE>
+__device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M, int N, int m_tiles, int n_tiles,
+                                              int total_tiles, int warp, int lane, uint32_t tmem_base, float* staging,
+                                              uint64_t* acc_full, uint64_t* acc_empty, volatile int* abort_flag,
+                                              tlnn_dev_err* err) {
+    constexpr int NCHUNK = BN / 32;
+    constexpr bool GENERIC = MODE == EPI_GENERIC;
+    constexpr bool HAS_OUT = MODE != EPI_ARGMAX;
+    const int ew = warp - 2;                        // 0..7
+    const int quarter = warp & 3;
+    const int half = ew >> 2;                       // 0: even chunks, 1: odd chunks
+    float* stage_tile = staging + ew * 1024;
+    const int sub_row = lane >> 3;                  // phase 2: row inside a group of four
+    const int c4 = lane & 7;                        // phase 2: 16-byte unit inside the 128-byte row segment
+
+    const bool has_bias = ep.bias != nullptr;
+    const bool has_res = MODE == EPI_F32_RES || (GENERIC && ep.residual != nullptr);
+    const bool want_argmax = MODE == EPI_ARGMAX || (GENERIC && ep.argmax_partials != nullptr);
+    const bool has_out = HAS_OUT && (!GENERIC || ep.out != nullptr);
+    const bool out_bf16 = MODE == EPI_BF16 || MODE == EPI_BF16_GELU || (GENERIC && ep.out_kind == TL_OUT_BF16);
+    const bool round_out = GENERIC && ep.out_kind == TL_OUT_TF32;
+    bool vec_ok = true;                              // specialised variants: guaranteed by the host
+    if (GENERIC) {
+        const int esz = out_bf16 ? 2 : 4;
+        vec_ok = has_out && ((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0) && ((ep.ldo * esz) % 16 == 0) &&
+                 (!has_res || (((reinterpret_cast<uintptr_t>(ep.residual) & 15u) == 0) && (ep.ldr % 4 == 0)));
+    }
+
+    int local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
+        const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+        const int buf = local & 1;
+        const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
+        const int n0 = tc.n_blk * BN;
+        const long long row_base = (long long)tc.m_blk * BM + quarter * 32;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+        // live chunks of this warp: half, half + 2, ... while the chunk starts inside N
+        int n_live = 0;
+        for (int c = half; c < NCHUNK && n0 + c * 32 < N; c += 2) n_live++;
+
+        float best = -INFINITY;
+        int best_i = 0x7fffffff;
+        bool waited = false;
+#pragma unroll 1
+        for (int i = 0; i < n_live; i++) {
+            const int chunk = half + 2 * i;
+            const int col0 = n0 + chunk * 32;
+            const int ncols = min(32, N - col0);
+            const bool full = ncols == 32;
+            const bool fast = vec_ok && full;
+            // requests that do not depend on the accumulator go out first
+            float bias_lane = 0.f;
+            if (has_bias && lane < ncols) bias_lane = __ldg(ep.bias + col0 + lane);
+            float4 res[8];
+            if (has_res && fast) {
+#pragma unroll
+                for (int it = 0; it < 8; it++) {
+                    const long long row = row_base + it * 4 + sub_row;
+                    long long rrow = row;
+                    if (GENERIC && ep.res_row_mod > 0) rrow = ep.res_row_off + row % ep.res_row_mod;
+                    res[it] = row < M ? *reinterpret_cast<const float4*>(ep.residual + rrow * ep.ldr + col0 + c4 * 4)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            if (!waited) {
+                if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 104)) return;
+                __syncwarp();
+                tc_fence_after();
+                waited = true;
+            }
+            uint32_t acc[32];
+            tmem_ld32_issue(taddr + (uint32_t)(chunk * 32), acc);
+            tmem_ld_wait();
+            if (i == n_live - 1) {
+                // every accumulator column this warp needs is in registers: hand the buffer back
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(acc[j]);
+            // ---- phase 1
+            if (has_bias) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
+            }
+            if (MODE == EPI_BF16_GELU) {
+                apply_act_chunk<false>(TLNN_ACT_GELU, v);
+            } else if (GENERIC && ep.act != TLNN_ACT_NONE) {
+                if (ep.accurate_math) apply_act_chunk<true>(ep.act, v);
+                else apply_act_chunk<false>(ep.act, v);
+            }
+            if (want_argmax) {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (j < ncols && v[j] > best) { best = v[j]; best_i = col0 + j; }
+            }
+            if (has_out) {
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    *reinterpret_cast<float4*>(stage_tile + lane * 32 + ((u ^ (lane & 7)) << 2)) =
+                        make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+                __syncwarp();
+                // ---- phase 2
+                if (fast) {
+#pragma unroll
+                    for (int it = 0; it < 8; it++) {
+                        const int rr = it * 4 + sub_row;
+                        const long long row = row_base + rr;
+                        float4 o = *reinterpret_cast<const float4*>(stage_tile + rr * 32 + ((c4 ^ (rr & 7)) << 2));
+                        if (has_res) { o.x += res[it].x; o.y += res[it].y; o.z += res[it].z; o.w += res[it].w; }
+                        if (row < M) {
+                            long long orow = row;
+                            if (GENERIC && ep.row_group > 0)
+                                orow = (row / ep.row_group) * ep.out_group + ep.out_off + row % ep.row_group;
+                            const long long off = orow * ep.ldo + col0 + c4 * 4;
+                            if (out_bf16) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(o.x, o.y);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(o.z, o.w);
+                                uint2 pk;
+                                pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                                pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(ep.out) + off) = pk;
+                            } else {
+                                if (round_out) {
+                                    o.x = round_tf32(o.x); o.y = round_tf32(o.y); o.z = round_tf32(o.z); o.w = round_tf32(o.w);
+                                }
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(ep.out) + off) = o;
+                            }
+                        }
+                    }
+                } else if (GENERIC) {
+                    // ragged or unaligned: one column per lane, one row per step - still whole row segments
+                    const bool col_ok = lane < ncols;
+#pragma unroll 1
+                    for (int rr = 0; rr < 32; rr++) {
+                        const long long row = row_base + rr;
+                        if (row >= M) break;
+                        float o = stage_tile[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))];
+                        if (col_ok) {
+                            if (has_res) {
+                                const long long rrow = ep.res_row_mod > 0 ? ep.res_row_off + row % ep.res_row_mod : row;
+                                o += ep.residual[rrow * ep.ldr + col0 + lane];
+                            }
+                            const long long orow = ep.row_group > 0
+                                ? (row / ep.row_group) * ep.out_group + ep.out_off + row % ep.row_group : row;
+                            const long long off = orow * ep.ldo + col0 + lane;
+                            if (out_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[off] = __float2bfloat16_rn(o);
+                            else reinterpret_cast<float*>(ep.out)[off] = round_out ? round_tf32(o) : o;
+                        }
+                    }
+                }
+                __syncwarp();     // the staging tile is rewritten by the next chunk
+            }
+        }
+        if (n_live == 0) {
+            // no live chunk in this tile: the MMA warp still needs this warp's arrival for the buffer
+            if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 105)) return;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        if (want_argmax) {
+            const long long my_row = row_base + lane;
+            // two warps cover a row: each leaves its own candidate, the reduce kernel takes the better one
+            if (my_row < M)
+                ep.argmax_partials[(my_row * n_tiles + tc.n_blk) * 2 + half] = make_float2(best, __int_as_float(best_i));
+        }
+    }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------------------------------
-template <int BN, bool TF32>
+template <int BN, bool TF32, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const tl_gemm_epilogue ep, int M, int N, int K, int m_tiles, int n_tiles, tlnn_dev_err* err) {
@@ -232,7 +456,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);      // one arrival per epilogue warp
+            mbar_init(&acc_empty[a], 8);      // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -300,125 +524,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
-        const int quarter = warp & 3;                 // TMEM lanes this warp may read: 32*quarter .. +31
-        const int elem_out = ep.out_kind == TL_OUT_BF16 ? 2 : 4;
-        const bool vec_out = ep.out != nullptr && ((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0) &&
-                             ((ep.ldo * elem_out) % 16 == 0);
-        const bool vec_res = ep.residual != nullptr && ((reinterpret_cast<uintptr_t>(ep.residual) & 15u) == 0) &&
-                             (ep.ldr % 4 == 0);
-        const bool vec_bias = ep.bias != nullptr && ((reinterpret_cast<uintptr_t>(ep.bias) & 15u) == 0);
-        int local = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
-            TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-            const int buf = local & 1;
-            const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-            if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 104)) break;
-            __syncwarp();
-            tc_fence_after();
-            const long long row = (long long)tc.m_blk * BM + quarter * 32 + lane;
-            const bool row_ok = row < M;
-            long long out_row = row, res_row = row;
-            if (ep.row_group > 0) out_row = (row / ep.row_group) * ep.out_group + ep.out_off + row % ep.row_group;
-            if (ep.res_row_mod > 0) res_row = ep.res_row_off + row % ep.res_row_mod;
-            const int n0 = tc.n_blk * BN;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-            float best = -INFINITY;
-            int best_i = 0x7fffffff;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                const int col0 = n0 + c0;
-                if (col0 >= N) break;                 // uniform over the CTA
-                float v[32];
-                __syncwarp();                         // tcgen05.ld is warp-collective: reconverge first
-                tmem_ld32(taddr + (uint32_t)c0, v);
-                if (row_ok) {
-                const int ncols = min(32, N - col0);
-                const bool full = ncols == 32;
-                if (ep.bias) {
-                    if (full && vec_bias) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 b = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j));
-                            v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) v[j] += __ldg(ep.bias + col0 + j);
-                    }
-                }
-                if (ep.act != TLNN_ACT_NONE) {
-                    if (ep.accurate_math) {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = apply_act<true>(ep.act, v[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = apply_act<false>(ep.act, v[j]);
-                    }
-                }
-                if (ep.residual) {
-                    const float* rp = ep.residual + res_row * ep.ldr + col0;
-                    if (full && vec_res) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 r = *reinterpret_cast<const float4*>(rp + j);
-                            v[j] += r.x; v[j + 1] += r.y; v[j + 2] += r.z; v[j + 3] += r.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) v[j] += rp[j];
-                    }
-                }
-                if (ep.argmax_partials) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (j < ncols && v[j] > best) { best = v[j]; best_i = col0 + j; }
-                }
-                if (ep.out) {
-                    if (ep.out_kind == TL_OUT_BF16) {
-                        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + out_row * ep.ldo + col0;
-                        if (full && vec_out) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 p;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                p.x = *reinterpret_cast<uint32_t*>(&h0);
-                                p.y = *reinterpret_cast<uint32_t*>(&h1);
-                                p.z = *reinterpret_cast<uint32_t*>(&h2);
-                                p.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(op + j) = p;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) if (j < ncols) op[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    } else {
-                        if (ep.out_kind == TL_OUT_TF32) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) v[j] = round_tf32(v[j]);
-                        }
-                        float* op = reinterpret_cast<float*>(ep.out) + out_row * ep.ldo + col0;
-                        if (full && vec_out) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) if (j < ncols) op[j] = v[j];
-                        }
-                    }
-                }
-                }   // row_ok
-            }
-            if (ep.argmax_partials && row_ok)
-                ep.argmax_partials[row * n_tiles + tc.n_blk] = make_float2(best, __int_as_float(best_i));
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
+        // ------------------------------------------------------------------ epilogue (8 warps, 128 rows x BN columns)
+        epilogue_warp<BN, MODE>(ep, M, N, m_tiles, n_tiles, total_tiles, warp, lane, tmem_base,
+                                reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err);
     }
 
     tc_fence_before();
@@ -478,9 +586,9 @@ int pick_bn(int M, int N, int sm_count) {
     return 64;
 }
 
-template <int BN, bool TF32>
+template <int BN, bool TF32, int MODE>
 int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep, int M, int N, int K) {
-    auto kernel = gemm_tcgen05_kernel<BN, TF32>;
+    auto kernel = gemm_tcgen05_kernel<BN, TF32, MODE>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM));
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     const long long total = (long long)m_tiles * n_tiles;
@@ -493,9 +601,45 @@ int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl
     return TLNN_OK;
 }
 
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The specialised epilogue that matches this description exactly, or EPI_GENERIC.
+int pick_mode(const tl_gemm_epilogue& ep, int N) {
+    const bool plain_rows = ep.row_group == 0 && ep.res_row_mod == 0;
+    if (ep.out == nullptr && ep.argmax_partials != nullptr && ep.residual == nullptr && ep.act == TLNN_ACT_NONE)
+        return EPI_ARGMAX;
+    if (!plain_rows || ep.argmax_partials != nullptr || ep.out == nullptr || N % 32 != 0 || !aligned16(ep.out))
+        return EPI_GENERIC;
+    if (ep.out_kind == TL_OUT_BF16 && ep.residual == nullptr && (ep.ldo * 2) % 16 == 0) {
+        if (ep.act == TLNN_ACT_NONE) return EPI_BF16;
+        if (ep.act == TLNN_ACT_GELU && !ep.accurate_math) return EPI_BF16_GELU;
+    }
+    if (ep.out_kind == TL_OUT_F32 && ep.residual != nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0 &&
+        aligned16(ep.residual) && ep.ldr % 4 == 0)
+        return EPI_F32_RES;
+    return EPI_GENERIC;
+}
+
+template <int BN>
+int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep,
+              int M, int N, int K) {
+    if (tf32) return launch<BN, true, EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);      // FP32/TF32 shapes are small
+    switch (mode) {
+        case EPI_BF16: return launch<BN, false, EPI_BF16>(ctx, ta, tb, ep, M, N, K);
+        case EPI_BF16_GELU: return launch<BN, false, EPI_BF16_GELU>(ctx, ta, tb, ep, M, N, K);
+        case EPI_F32_RES: return launch<BN, false, EPI_F32_RES>(ctx, ta, tb, ep, M, N, K);
+        case EPI_ARGMAX: return launch<BN, false, EPI_ARGMAX>(ctx, ta, tb, ep, M, N, K);
+        default: return launch<BN, false, EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);
+    }
+}
+
 }  // namespace
 
 int tl_gemm_bn(int M, int N, int sm_count) { return pick_bn(M, N, sm_count); }
+int tl_gemm_argmax_parts(int M, int N, int sm_count) {
+    const int bn = pick_bn(M, N, sm_count);
+    return 2 * ((N + bn - 1) / bn);     // two epilogue warps cover each row of a tile
+}
 
 int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w, long long ldw, int M, int N, int K,
             const tl_gemm_epilogue& ep) {
@@ -510,7 +654,8 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
     TL_TRY(make_map(&ta, prec, a, M, K, lda, BM));
     TL_TRY(make_map(&tb, prec, w, N, K, ldw, bn));
     const bool tf32 = prec == TLNN_PREC_TF32;
-    if (bn == 256) return tf32 ? launch<256, true>(ctx, ta, tb, ep, M, N, K) : launch<256, false>(ctx, ta, tb, ep, M, N, K);
-    if (bn == 128) return tf32 ? launch<128, true>(ctx, ta, tb, ep, M, N, K) : launch<128, false>(ctx, ta, tb, ep, M, N, K);
-    return tf32 ? launch<64, true>(ctx, ta, tb, ep, M, N, K) : launch<64, false>(ctx, ta, tb, ep, M, N, K);
+    const int mode = pick_mode(ep, N);
+    if (bn == 256) return launch_bn<256>(ctx, tf32, mode, ta, tb, ep, M, N, K);
+    if (bn == 128) return launch_bn<128>(ctx, tf32, mode, ta, tb, ep, M, N, K);
+    return launch_bn<64>(ctx, tf32, mode, ta, tb, ep, M, N, K);
 }
