@@ -11,6 +11,7 @@
 //  * float32 path: CUDA-core kernel in exact float32 arithmetic (one warp per query, keys across lanes) for the
 //    FP32/TF32 mode, where the shapes are small (T <= 128, hd 32) and operand rounding would eat the tolerance.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -364,6 +365,19 @@ int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H,
 
 }  // namespace
 
+int tl_attention_tcgen05(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16* out, int B, int T, int heads, int causal);
+
+// TLNN_ATTENTION=legacy forces the mma.sync kernel, =tcgen05 forces the TMEM kernel (head dimension 64 only);
+// by default the TMEM kernel takes sequences of at least 192 tokens.
+static int attention_choice() {
+    static int choice = -1;
+    if (choice < 0) {
+        const char* e = getenv("TLNN_ATTENTION");
+        choice = !e ? 0 : (strcmp(e, "legacy") == 0 ? 1 : (strcmp(e, "tcgen05") == 0 ? 2 : 0));
+    }
+    return choice;
+}
+
 int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int out_kind, int B, int T, int heads, int hd,
                       int causal) {
     if (B == 0 || T == 0) return TLNN_OK;
@@ -372,6 +386,8 @@ int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int o
         TL_REQUIRE(out_kind == TL_OUT_BF16, "attention: the bf16 path writes bf16");
         const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(qkv);
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+        const int choice = attention_choice();
+        if (hd == 64 && choice != 1 && (choice == 2 || T >= 192)) return tl_attention_tcgen05(ctx, q, o, B, T, heads, causal);
         if (hd == 32) return launch_bf16<32>(ctx, q, o, B, T, heads, causal);
         if (hd == 64) return launch_bf16<64>(ctx, q, o, B, T, heads, causal);
         if (hd == 128) return launch_bf16<128>(ctx, q, o, B, T, heads, causal);

@@ -15,18 +15,17 @@
 // Every wait on an mbarrier is bounded by wall-clock time; on expiry the kernel records TLNN_ERR_TIMEOUT in the
 // context's error word, raises a CTA-wide abort flag, and all roles fall through to the common exit, where the
 // TMEM allocation is returned.
-#include "common.cuh"
-
-#include <cuda.h>   // CUtensorMap and enums only; the encode entry point is fetched through the runtime
+#include "sm100_ptx.cuh"
 
 namespace {
+
+using namespace sm100;
 
 constexpr int BM = 128;             // UMMA M (cta_group::1)
 constexpr int ROW_BYTES = 128;      // one swizzle-128B row of K: 64 bf16 or 32 float32
 constexpr int MMA_K_BYTES = 32;     // K extent of one tcgen05.mma: 16 bf16 or 8 tf32
 constexpr int GROUP_M = 8;          // rasterisation: tiles are walked in groups of GROUP_M row-blocks
 constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, eight epilogue warps
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 template <int BN> struct Cfg {
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
@@ -38,121 +37,6 @@ template <int BN> struct Cfg {
     static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;     // eight 4 KB staging tiles
     static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024 /*alignment slack*/;
 };
-
-// ---- PTX wrappers -------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns false (after recording the failure and raising the CTA's abort flag) when the barrier
-// did not flip within WAIT_LIMIT_NS or another role of this CTA already gave up.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            tlnn_dev_err* err, int site) {
-    unsigned long long t0 = globaltimer_ns();
-    for (;;) {
-        for (int i = 0; i < 128; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            tl_dev_fail(err, TLNN_ERR_TIMEOUT, site, (long long)blockIdx.x);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          tlnn_dev_err* err, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, err, site);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-template <bool TF32>
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (TF32) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-            : "memory");
-    }
-}
-// Arrive on an mbarrier once every tcgen05 operation issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
-// The load is split in two: request the chunk, and later wait for every outstanding request of this thread.  The
-// destination registers must not be read between the two.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes
-// apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;                  // leading byte offset (ignored for swizzled K-major), canonical value 1
-    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
-    d |= (uint64_t)1 << 46;                  // version
-    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
-    return d;
-}
 
 // Instruction descriptor: D float32, A/B bf16 (1) or tf32 (2), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
 template <int BN, bool TF32>
@@ -539,45 +423,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// 2-D map over a (rows, K) matrix with K contiguous and a pitch of ld elements; box = 128 bytes of K x box_rows.
-int make_map(CUtensorMap* map, int prec, const void* base, long long rows, long long K, long long ld, int box_rows) {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) {
-        tl_set_error("cuTensorMapEncodeTiled is not available from the driver");
-        return TLNN_ERR_CUDA;
-    }
-    const int esz = prec == TLNN_PREC_BF16 ? 2 : 4;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(ld * esz)};
-    cuuint32_t box[2] = {(cuuint32_t)(ROW_BYTES / esz), (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, prec == TLNN_PREC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                    2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        tl_set_error("cuTensorMapEncodeTiled failed with %d (rows=%lld K=%lld ld=%lld box_rows=%d)", (int)r, rows, K, ld,
-                     box_rows);
-        return TLNN_ERR_CUDA;
-    }
-    return TLNN_OK;
-}
-
 int pick_bn(int M, int N, int sm_count) {
     const int m_tiles = (M + BM - 1) / BM;
     if (N > 128 && (long long)m_tiles * ((N + 255) / 256) >= sm_count) return 256;
@@ -651,11 +496,54 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
     TL_REQUIRE(((uintptr_t)a & 15u) == 0 && ((uintptr_t)w & 15u) == 0, "gemm: operands must be 16-byte aligned");
     const int bn = pick_bn(M, N, ctx->sm_count);
     CUtensorMap ta, tb;
-    TL_TRY(make_map(&ta, prec, a, M, K, lda, BM));
-    TL_TRY(make_map(&tb, prec, w, N, K, ldw, bn));
+    TL_TRY(make_tile_map(&ta, prec == TLNN_PREC_BF16, a, M, K, lda, BM));
+    TL_TRY(make_tile_map(&tb, prec == TLNN_PREC_BF16, w, N, K, ldw, bn));
     const bool tf32 = prec == TLNN_PREC_TF32;
     const int mode = pick_mode(ep, N);
     if (bn == 256) return launch_bn<256>(ctx, tf32, mode, ta, tb, ep, M, N, K);
     if (bn == 128) return launch_bn<128>(ctx, tf32, mode, ta, tb, ep, M, N, K);
     return launch_bn<64>(ctx, tf32, mode, ta, tb, ep, M, N, K);
 }
+
+// ---- tensor-map encoding (shared with the attention kernel) ---------------------------------------------------------
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+}  // namespace
+
+int sm100::make_tile_map(CUtensorMap* map, bool bf16, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        tl_set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return TLNN_ERR_CUDA;
+    }
+    const int esz = bf16 ? 2 : 4;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld * esz)};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                    2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_set_error("cuTensorMapEncodeTiled failed with %d (rows=%lld K=%lld ld=%lld box_rows=%d)", (int)r, rows, K, ld,
+                     box_rows);
+        return TLNN_ERR_CUDA;
+    }
+    return TLNN_OK;
+}
+
