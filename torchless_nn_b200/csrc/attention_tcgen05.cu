@@ -1,16 +1,17 @@
 // Fused attention on the sm_100a tensor cores (bf16, head dimension 64).
 //
 // One CTA owns 256 consecutive queries of one (batch, head) as two independent 128-row streams.  Roles by warp:
-//   warps 0-3  softmax of stream 0 (thread = query row: the S tile is read from TMEM one row per thread, so the row
+//   warps 0-3  softmax of stream 0 (thread = query row: a score row is read from TMEM by one thread, so the row
 //              maximum and the row sum need no shuffles), warps 4-7 the same for stream 1;
-//   warp 8     MMA issuer (one thread): S = Q K^T with tcgen05.mma (128 x 128 x 64) into TMEM, and O_j = P V
-//              (128 x 64 x 128) with P taken from shared memory and V read as an MN-major operand;
-//   warp 9     TMA producer: Q once, then K / V tiles of 128 keys through a three-stage ring.
-// Per stream and key tile j the tensor core runs [P_{j-1} V_{j-1}, Q K_j^T] and then the stream's softmax warps turn
-// S_j into P_j (bf16, written straight into the swizzled operand layout) while folding the partial product O_{j-1}
-// into their float32 running output: O = (O + O_{j-1}) * 2^(m_{j-1} - m_j).  The two streams alternate on the tensor
-// core, so one stream's exponentials overlap the other stream's MMAs.  The decoder mask is an index comparison.
-// All mbarrier waits are bounded in time; on expiry the kernel records TLNN_ERR_TIMEOUT and every role leaves.
+//   warp 8     MMA issuer (one thread): S_j = Q K_j^T (128 x 64 x 64) into one of the stream's two S buffers in TMEM,
+//              and O += P_j V_j (128 x 64 x 64) with P taken from shared memory and V read as an MN-major operand;
+//   warp 9     TMA producer: Q once, then K / V tiles of 64 keys through a six-stage ring.
+// S is double-buffered per stream, so S_{j+1} and S_{j+2} are computed while the softmax warps work on S_j; the
+// softmax of a tile waits only for its own S (and, rarely, for the accumulator to be quiescent), never for the P V
+// product of the previous tile.  O accumulates in TMEM across tiles; probabilities are taken against a reference
+// maximum that is moved (and O, l rescaled in TMEM) only when the true row maximum has grown by more than 2^8, which is
+// exact after the final division by l.  The decoder mask is an index comparison.
+// All waits are bounded in time; on expiry the kernel records TLNN_ERR_TIMEOUT and every role leaves.
 #include "sm100_ptx.cuh"
 
 namespace {
@@ -19,19 +20,19 @@ using namespace sm100;
 
 constexpr int HD = 64;                 // head dimension
 constexpr int BQ = 128;                // query rows per stream
-constexpr int BK = 128;                // keys per tile
-constexpr int KV_STAGES = 3;
+constexpr int BK = 64;                 // keys per tile
+constexpr int KV_STAGES = 6;
 constexpr int AT_THREADS = 320;
 constexpr uint32_t Q_BYTES = BQ * HD * 2;          // 16 KB per stream
-constexpr uint32_t K_BYTES = BK * HD * 2;          // 16 KB
-constexpr uint32_t V_BYTES = BK * HD * 2;          // 16 KB
-constexpr uint32_t P_BYTES = BQ * BK * 2;          // 32 KB per stream: two 64-key blocks of 128 rows x 128 bytes
+constexpr uint32_t K_BYTES = BK * HD * 2;          // 8 KB
+constexpr uint32_t V_BYTES = BK * HD * 2;          // 8 KB
+constexpr uint32_t P_BYTES = BQ * BK * 2;          // 16 KB: 128 rows x 128 bytes, one swizzle block
 constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_KV = OFF_Q + 2 * Q_BYTES;
-constexpr uint32_t OFF_P = OFF_KV + KV_STAGES * (K_BYTES + V_BYTES);
-constexpr uint32_t OFF_BAR = OFF_P + 2 * P_BYTES;
-constexpr size_t AT_SMEM = OFF_BAR + 256 + 1024;   // barriers + alignment slack
-constexpr uint32_t TMEM_COLS = 512;                // S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
+constexpr uint32_t OFF_P = OFF_KV + KV_STAGES * (K_BYTES + V_BYTES);      // P[stream][buffer]
+constexpr uint32_t OFF_BAR = OFF_P + 4 * P_BYTES;
+constexpr size_t AT_SMEM = OFF_BAR + 512 + 1024;   // barriers + alignment slack
+constexpr uint32_t TMEM_COLS = 512;                // S[s][b] at 128 s + 64 b, O[s] at 256 + 64 s
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -39,24 +40,25 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Instruction descriptors: D float32, A and B bf16, M = 128.  S: N = 128, both operands K-major.  PV: N = 64, A
-// K-major (P), B MN-major (V rows are keys, the head dimension is contiguous).
+// Instruction descriptors: D float32, A and B bf16, M = 128, N = 64.  S: both operands K-major.  PV: A K-major (P),
+// B MN-major (V rows are keys, the head dimension is contiguous).
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                               ((uint32_t)(BQ >> 4) << 24);
 
 template <bool CAUSAL>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __restrict__ out, int T, int H,
-                         float scale_log2, tlnn_dev_err* err) {
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                         __nv_bfloat16* __restrict__ out, int T, int H, float scale_log2, tlnn_dev_err* err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* kv_full = q_full + 1;                  // [KV_STAGES]
     uint64_t* kv_empty = kv_full + KV_STAGES;        // [KV_STAGES]
-    uint64_t* mma_done = kv_empty + KV_STAGES;       // [2] per stream: S_j (and O_{j-1}) are in TMEM
-    uint64_t* p_full = mma_done + 2;                 // [2] per stream: P_j is in shared memory, S_j and O_{j-1} consumed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2);
+    uint64_t* s_full = kv_empty + KV_STAGES;         // [2][2] S_j is in TMEM buffer j & 1
+    uint64_t* p_full = s_full + 4;                   // [2][2] P_j is in shared-memory buffer j & 1 (and S_j has been read)
+    uint64_t* pv_done = p_full + 4;                  // [2][2] O includes P_j V_j (and P buffer j & 1 may be rewritten)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -66,20 +68,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat
     const int q0 = q_blk * 2 * BQ;
     const int row0 = b * T;                                // first row of this sequence in the packed (B*T, 3d) buffer
     const int tiles_all = (T + BK - 1) / BK;
-    // key tiles each stream needs: causal rows q see keys <= q
-    int n_tiles[2];
-#pragma unroll
-    for (int s = 0; s < 2; s++) {
-        const int qs = q0 + s * BQ;
-        n_tiles[s] = qs >= T ? 0 : (CAUSAL ? min(tiles_all, qs / BK + 1) : tiles_all);
-    }
-    const int n_max = max(n_tiles[0], n_tiles[1]);
+    // key tiles per stream: causal rows q see keys <= q
+    const int qs1 = q0 + BQ;
+    const int nt0 = q0 >= T ? 0 : (CAUSAL ? min(tiles_all, (q0 + BQ - 1) / BK + 1) : tiles_all);
+    const int nt1 = qs1 >= T ? 0 : (CAUSAL ? min(tiles_all, (qs1 + BQ - 1) / BK + 1) : tiles_all);
+    const int n_max = max(nt0, nt1);
 
     if (threadIdx.x == 0) {
-        tma_prefetch_desc(&tm_qkv);
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_kv);
         mbar_init(q_full, 1);
         for (int i = 0; i < KV_STAGES; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&mma_done[s], 1); mbar_init(&p_full[s], 4); }
+        for (int i = 0; i < 4; i++) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -98,66 +98,88 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             mbar_expect_tx(q_full, 2 * Q_BYTES);
-            tma_load_2d(smem_u32(smem + OFF_Q), &tm_qkv, smem_u32(q_full), h * HD, row0 + q0);
-            tma_load_2d(smem_u32(smem + OFF_Q + Q_BYTES), &tm_qkv, smem_u32(q_full), h * HD, row0 + q0 + BQ);
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int j = 0; j < n_max; j++) {
+            tma_load_2d(smem_u32(smem + OFF_Q), &tm_q, smem_u32(q_full), h * HD, row0 + q0);
+            tma_load_2d(smem_u32(smem + OFF_Q + Q_BYTES), &tm_q, smem_u32(q_full), h * HD, row0 + q0 + BQ);
+            for (int t = 0; t < n_max; t++) {
+                const int stage = t % KV_STAGES;
+                const uint32_t phase = (uint32_t)(t / KV_STAGES) & 1u;
                 if (!mbar_wait(&kv_empty[stage], phase ^ 1u, abort_flag, err, 201)) break;
                 const uint32_t sk = smem_u32(smem + OFF_KV + stage * (K_BYTES + V_BYTES));
                 const uint32_t bar = smem_u32(&kv_full[stage]);
                 mbar_expect_tx(&kv_full[stage], K_BYTES + V_BYTES);
-                tma_load_2d(sk, &tm_qkv, bar, d + h * HD, row0 + j * BK);
-                tma_load_2d(sk + K_BYTES, &tm_qkv, bar, 2 * d + h * HD, row0 + j * BK);
-                if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
+                tma_load_2d(sk, &tm_kv, bar, d + h * HD, row0 + t * BK);
+                tma_load_2d(sk + K_BYTES, &tm_kv, bar, 2 * d + h * HD, row0 + t * BK);
             }
         }
     } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ MMA issuer: one thread serves both streams
         if (lane == 0) {
             bool ok = mbar_wait(q_full, 0, abort_flag, err, 202);
             tc_fence_after();
-            int stage = 0, prev_stage = 0;
-            uint32_t phase = 0;
-            // iteration j issues, per stream, P_{j-1} V_{j-1} (if any) and then Q K_j^T (if any)
-            for (int j = 0; j <= n_max && ok; j++) {
-                if (j < n_max) {
-                    if (!mbar_wait(&kv_full[stage], phase, abort_flag, err, 203)) { ok = false; break; }
-                    tc_fence_after();
-                }
-                const uint32_t sk = smem_u32(smem + OFF_KV + stage * (K_BYTES + V_BYTES));
-                const uint32_t sv_prev = smem_u32(smem + OFF_KV + prev_stage * (K_BYTES + V_BYTES) + K_BYTES);
+            const int nt[2] = {nt0, nt1};
+            int s_issued[2] = {0, 0};       // S tiles issued per stream
+            int pv_issued[2] = {0, 0};      // P V products issued per stream
+            int kv_ready = 0;               // key tiles known to be in shared memory
+            int released = 0;               // key tiles handed back to the producer
+            unsigned long long idle_since = 0;
+            while (ok && (pv_issued[0] < nt[0] || pv_issued[1] < nt[1])) {
+                bool progress = false;
 #pragma unroll
                 for (int s = 0; s < 2; s++) {
-                    if (j > n_tiles[s] || n_tiles[s] == 0) continue;
-                    if (j > 0) {
-                        // P_{j-1} of this stream is complete (which also means S_{j-1} and O_{j-2} have been consumed)
-                        if (!mbar_wait(&p_full[s], (uint32_t)(j - 1) & 1u, abort_flag, err, 204)) { ok = false; break; }
+                    // keep up to two score tiles ahead of the products
+                    while (ok && s_issued[s] < nt[s] && s_issued[s] < pv_issued[s] + 2) {
+                        const int j = s_issued[s];
+                        while (ok && kv_ready <= j) {
+                            if (!mbar_wait(&kv_full[kv_ready % KV_STAGES], (uint32_t)(kv_ready / KV_STAGES) & 1u, abort_flag, err, 203)) ok = false;
+                            else kv_ready++;
+                        }
+                        if (!ok) break;
                         tc_fence_after();
-                        const uint32_t sp = smem_u32(smem + OFF_P + s * P_BYTES);
-                        const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * HD);
-#pragma unroll
-                        for (int kk = 0; kk < BK / 16; kk++) {
-                            // A: P rows x 16 keys inside 64-key block kk / 4; B: 16 key rows of V (2048 bytes per step)
-                            const uint64_t a_desc = make_smem_desc(sp + (uint32_t)(kk >> 2) * (BQ * 128) + (uint32_t)(kk & 3) * 32);
-                            const uint64_t b_desc = make_smem_desc(sv_prev + (uint32_t)kk * 2048);
-                            umma<false>(o_tmem, a_desc, b_desc, IDESC_PV, kk != 0 ? 1u : 0u);
-                        }
-                    }
-                    if (j < n_tiles[s]) {
                         const uint32_t sq = smem_u32(smem + OFF_Q + s * Q_BYTES);
-                        const uint32_t s_tmem = tmem_base + (uint32_t)(s * BK);
+                        const uint32_t sk = smem_u32(smem + OFF_KV + (j % KV_STAGES) * (K_BYTES + V_BYTES));
+                        const uint32_t s_tmem = tmem_base + (uint32_t)(s * 128 + (j & 1) * 64);
 #pragma unroll
-                        for (int k = 0; k < HD / 16; k++) {
+                        for (int k = 0; k < HD / 16; k++)
                             umma<false>(s_tmem, make_smem_desc(sq + k * 32), make_smem_desc(sk + k * 32), IDESC_S, k != 0 ? 1u : 0u);
+                        umma_commit(&s_full[s * 2 + (j & 1)]);
+                        s_issued[s]++;
+                        progress = true;
+                    }
+                    if (ok && pv_issued[s] < nt[s]) {
+                        const int j = pv_issued[s];
+                        if (mbar_test_wait(&p_full[s * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u)) {
+                            tc_fence_after();
+                            const uint32_t sp = smem_u32(smem + OFF_P + (s * 2 + (j & 1)) * P_BYTES);
+                            const uint32_t sv = smem_u32(smem + OFF_KV + (j % KV_STAGES) * (K_BYTES + V_BYTES) + K_BYTES);
+                            const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * HD);
+#pragma unroll
+                            for (int kk = 0; kk < BK / 16; kk++)
+                                umma<false>(o_tmem, make_smem_desc(sp + kk * 32), make_smem_desc(sv + kk * 2048), IDESC_PV,
+                                            (j > 0 || kk != 0) ? 1u : 0u);
+                            umma_commit(&pv_done[s * 2 + (j & 1)]);
+                            pv_issued[s]++;
+                            progress = true;
+                            // a key tile goes back to the producer once every stream that needs it has used its V
+                            while (released < n_max && (released >= nt[0] || pv_issued[0] > released) &&
+                                   (released >= nt[1] || pv_issued[1] > released)) {
+                                umma_commit(&kv_empty[released % KV_STAGES]);
+                                released++;
+                            }
                         }
                     }
-                    umma_commit(&mma_done[s]);
                 }
-                if (!ok) break;
-                if (j > 0) umma_commit(&kv_empty[prev_stage]);      // K_{j-1} and V_{j-1} are no longer needed
-                prev_stage = stage;
-                if (j < n_max) { if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; } }
+                if (progress) {
+                    idle_since = 0;
+                } else {
+                    if (*abort_flag) { ok = false; break; }
+                    const unsigned long long now = globaltimer_ns();
+                    if (idle_since == 0) idle_since = now;
+                    else if (now - idle_since > WAIT_LIMIT_NS) {
+                        *abort_flag = 1;
+                        tl_dev_fail(err, TLNN_ERR_TIMEOUT, 204, (long long)blockIdx.x);
+                        ok = false;
+                    }
+                }
             }
         }
     } else {
@@ -166,100 +188,102 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat
         const int quarter = warp & 3;                     // TMEM lanes 32*quarter .. +31
         const int r = quarter * 32 + lane;                // row inside the stream's tile
         const int q_row = q0 + s * BQ + r;                // query index in the sequence
-        const int nt = n_tiles[s];
-        const uint32_t s_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(s * BK);
-        const uint32_t o_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)(s * HD);
-        uint8_t* p_row = smem + OFF_P + s * P_BYTES + r * 128;
-        float o_acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        const int warp_row_lo = q0 + s * BQ + quarter * 32;
+        const int nt = s == 0 ? nt0 : nt1;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t o_tmem = tmem_base + lane_base + 256u + (uint32_t)(s * HD);
+        // Running statistics.  m_ref is the reference maximum the probabilities and the TMEM accumulator are currently
+        // expressed against (log2 units); it moves - and O and l are rescaled - only when the true row maximum has
+        // grown by more than 2^8 since, so most tiles do not touch O.
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < nt && ok; j++) {
-            if (!mbar_wait(&mma_done[s], (uint32_t)j & 1u, abort_flag, err, 205)) { ok = false; break; }
+            const int bsel = j & 1;
+            const uint32_t par = (uint32_t)(j >> 1) & 1u;
+            if (!mbar_wait(&s_full[s * 2 + bsel], par, abort_flag, err, 205)) { ok = false; break; }
             __syncwarp();
             tc_fence_after();
             const int k0 = j * BK;
-            const bool need_mask = (k0 + BK > T) || (CAUSAL && k0 + BK - 1 > q0 + s * BQ + quarter * 32);
-            // pass 1: row maximum
-            float mx = -INFINITY;
+            const bool need_mask = (k0 + BK > T) || (CAUSAL && k0 + BK - 1 > warp_row_lo);
+            uint32_t sc[BK];
+            const uint32_t s_tmem = tmem_base + lane_base + (uint32_t)(s * 128 + bsel * 64);
+            tmem_ld32_issue(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
+            tmem_ld32_issue(s_tmem + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
+            tmem_ld_wait();
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BK; i++) {
+                    const int key = k0 + i;
+                    if (key >= T || (CAUSAL && key > q_row)) sc[i] = 0xff800000u;      // -inf
+                }
+            }
+            // eight independent partial maxima, then a tree: no 64-long dependency chain
+            float mp[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) mp[i] = __uint_as_float(sc[i]);
+#pragma unroll
+            for (int i = 8; i < BK; i++) mp[i & 7] = fmaxf(mp[i & 7], __uint_as_float(sc[i]));
+            const float mx = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])), fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
+            // tile 0 holds key 0, visible to every row, so m_ref is finite from the first tile on; a later tile whose
+            // keys are all masked for this row leaves it unchanged
+            const float m_new = fmaxf(m_ref, mx * scale_log2);
+            const bool grow = m_new - m_ref > 8.f;                       // also true while m_ref is still -inf
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? ex2(m_ref - m_new) : 1.f;      // 0 on the first tile
+                if (grow) m_ref = m_new;
+                l_run *= alpha;
+                if (j > 0) {
+                    // the accumulator must be quiescent: P_{j-1} V_{j-1} is the last product issued for this stream
+                    if (!mbar_wait(&pv_done[s * 2 + ((j - 1) & 1)], (uint32_t)((j - 1) >> 1) & 1u, abort_flag, err, 206)) { ok = false; break; }
+                    __syncwarp();
+                    tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < BK / 32; c++) {
-                uint32_t acc[32];
-                tmem_ld32_issue(s_tmem + (uint32_t)(c * 32), acc);
-                tmem_ld_wait();
-                if (need_mask) {
+                    for (int c = 0; c < HD / 32; c++) {
+                        uint32_t acc[32];
+                        tmem_ld32_issue(o_tmem + (uint32_t)(c * 32), acc);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int key = k0 + c * 32 + i;
-                        const bool dead = key >= T || (CAUSAL && key > q_row);
-                        mx = dead ? mx : fmaxf(mx, __uint_as_float(acc[i]));
+                        for (int i = 0; i < 32; i++) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+                        tmem_st32(o_tmem + (uint32_t)(c * 32), acc);
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(acc[i]));
+                    tmem_st_wait();
                 }
             }
-            const float m_new = fmaxf(m_run, mx * scale_log2);     // finite: every processed tile has a live key per row
-            const float alpha = ex2(m_run - m_new);
-            // fold the previous tile's partial product, then rescale to the new maximum
-            if (j > 0) {
-#pragma unroll
-                for (int c = 0; c < HD / 32; c++) {
-                    uint32_t acc[32];
-                    tmem_ld32_issue(o_tmem + (uint32_t)(c * 32), acc);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o_acc[c * 32 + i] = (o_acc[c * 32 + i] + __uint_as_float(acc[i])) * alpha;
-                }
+            // the P buffer of this parity was last read by P_{j-2} V_{j-2}
+            if (j >= 2) {
+                if (!mbar_wait(&pv_done[s * 2 + bsel], (uint32_t)((j - 2) >> 1) & 1u, abort_flag, err, 207)) { ok = false; break; }
             }
-            l_run *= alpha;
-            m_run = m_new;
-            // pass 2: probabilities, row sum, bf16 P into the K-major 128-byte-swizzled operand layout
-            float l_add = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BK / 32; c++) {
-                uint32_t acc[32];
-                tmem_ld32_issue(s_tmem + (uint32_t)(c * 32), acc);
-                tmem_ld_wait();
-                float p[32];
+            // probabilities against the reference, row sum, bf16 P into the K-major 128-byte-swizzled operand layout
+            uint8_t* p_row = smem + OFF_P + (s * 2 + bsel) * P_BYTES + r * 128;
+            float lp[8];
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float e = ex2(fmaf(__uint_as_float(acc[i]), scale_log2, -m_new));
-                    if (need_mask) {
-                        const int key = k0 + c * 32 + i;
-                        if (key >= T || (CAUSAL && key > q_row)) e = 0.f;
-                    }
-                    p[i] = e;
-                    l_add += e;
-                }
-                // keys c*32 .. c*32+31 live in 64-key block c / 2, 16-byte units (c & 1) * 4 .. + 3 of this row
-                uint8_t* blk = p_row + (c >> 1) * (BQ * 128);
+            for (int g = 0; g < 8; g++) {
+                float pv[8];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    uint4 pk;
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p[8 * u + 0], p[8 * u + 1]);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(p[8 * u + 2], p[8 * u + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p[8 * u + 4], p[8 * u + 5]);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(p[8 * u + 6], p[8 * u + 7]);
-                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                    const int unit = ((c & 1) * 4 + u) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(blk + unit * 16) = pk;
-                }
+                for (int i = 0; i < 8; i++) pv[i] = ex2(fmaf(__uint_as_float(sc[g * 8 + i]), scale_log2, -m_ref));
+                lp[g] = ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(pv[2], pv[3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(pv[4], pv[5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(pv[6], pv[7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                // keys 8g .. 8g+7: 16-byte unit g of the row, XOR-swizzled by the row
+                *reinterpret_cast<uint4*>(p_row + ((g ^ (r & 7)) << 4)) = pk;
             }
-            l_run += l_add;
-            // make P visible to the tensor core (async proxy), order the TMEM reads, then hand over
+            l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
+            // make P visible to the tensor core (async proxy), order the TMEM accesses, then hand over
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[s]);
+            if (lane == 0) mbar_arrive(&p_full[s * 2 + bsel]);
         }
         if (ok && nt > 0) {
-            // the last partial product
-            if (mbar_wait(&mma_done[s], (uint32_t)nt & 1u, abort_flag, err, 206)) {
+            // the accumulator after the last product
+            if (mbar_wait(&pv_done[s * 2 + ((nt - 1) & 1)], (uint32_t)((nt - 1) >> 1) & 1u, abort_flag, err, 208)) {
                 __syncwarp();
                 tc_fence_after();
                 const float inv = 1.f / l_run;
@@ -272,14 +296,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat
                     if (q_row < T) {
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            float v[8];
-#pragma unroll
-                            for (int i = 0; i < 8; i++) v[i] = (o_acc[c * 32 + u * 8 + i] + __uint_as_float(acc[u * 8 + i])) * inv;
                             uint4 pk;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 0]) * inv, __uint_as_float(acc[u * 8 + 1]) * inv);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 2]) * inv, __uint_as_float(acc[u * 8 + 3]) * inv);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 4]) * inv, __uint_as_float(acc[u * 8 + 5]) * inv);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 6]) * inv, __uint_as_float(acc[u * 8 + 7]) * inv);
                             pk.x = *reinterpret_cast<uint32_t*>(&h0);
                             pk.y = *reinterpret_cast<uint32_t*>(&h1);
                             pk.z = *reinterpret_cast<uint32_t*>(&h2);
@@ -309,18 +330,19 @@ int tl_attention_tcgen05(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16*
     const long long rows = (long long)B * T;
     TL_REQUIRE(rows < (1ll << 31), "attention: too many rows");
     TL_REQUIRE(((uintptr_t)qkv & 15u) == 0 && ((uintptr_t)out & 15u) == 0, "attention: buffers must be 16-byte aligned");
-    CUtensorMap tm;
-    TL_TRY(make_tile_map(&tm, true, qkv, rows, 3ll * d, 3ll * d, BQ));
+    CUtensorMap tq, tkv;
+    TL_TRY(make_tile_map(&tq, true, qkv, rows, 3ll * d, 3ll * d, BQ));
+    TL_TRY(make_tile_map(&tkv, true, qkv, rows, 3ll * d, 3ll * d, BK));
     dim3 grid((T + 2 * BQ - 1) / (2 * BQ), B * heads);
     const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
     if (causal) {
         auto k = attention_tcgen05_kernel<true>;
         TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM));
-        TL_LAUNCH(ctx, "attention_tc_causal", k<<<grid, AT_THREADS, AT_SMEM, ctx->stream>>>(tm, out, T, heads, scale_log2, ctx->d_err));
+        TL_LAUNCH(ctx, "attention_tc_causal", k<<<grid, AT_THREADS, AT_SMEM, ctx->stream>>>(tq, tkv, out, T, heads, scale_log2, ctx->d_err));
     } else {
         auto k = attention_tcgen05_kernel<false>;
         TL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM));
-        TL_LAUNCH(ctx, "attention_tc_full", k<<<grid, AT_THREADS, AT_SMEM, ctx->stream>>>(tm, out, T, heads, scale_log2, ctx->d_err));
+        TL_LAUNCH(ctx, "attention_tc_full", k<<<grid, AT_THREADS, AT_SMEM, ctx->stream>>>(tq, tkv, out, T, heads, scale_log2, ctx->d_err));
     }
     return TLNN_OK;
 }
