@@ -3,9 +3,10 @@
 // One CTA owns 256 consecutive queries of one (batch, head) as two independent 128-row streams.  Roles by warp:
 //   warps 0-3  softmax of stream 0 (thread = query row: a score row is read from TMEM by one thread, so the row
 //              maximum and the row sum need no shuffles), warps 4-7 the same for stream 1;
-//   warp 8     MMA issuer (one thread): S_j = Q K_j^T (128 x 64 x 64) into one of the stream's two S buffers in TMEM,
-//              and O += P_j V_j (128 x 64 x 64) with P taken from shared memory and V read as an MN-major operand;
-//   warp 9     TMA producer: Q once, then K / V tiles of 64 keys through a six-stage ring.
+//   warps 8-9  MMA issuers, one thread per stream: S_j = Q K_j^T (128 x 64 x 64) into one of the stream's two S
+//              buffers in TMEM, and O += P_j V_j (128 x 64 x 64) with P taken from shared memory and V read as an
+//              MN-major operand;
+//   warp 10    TMA producer: Q once, then K / V tiles of 64 keys through a six-stage ring.
 // S is double-buffered per stream, so S_{j+1} and S_{j+2} are computed while the softmax warps work on S_j; the
 // softmax of a tile waits only for its own S (and, rarely, for the accumulator to be quiescent), never for the P V
 // product of the previous tile.  O accumulates in TMEM across tiles; probabilities are taken against a reference
@@ -22,7 +23,7 @@ constexpr int HD = 64;                 // head dimension
 constexpr int BQ = 128;                // query rows per stream
 constexpr int BK = 64;                 // keys per tile
 constexpr int KV_STAGES = 6;
-constexpr int AT_THREADS = 320;
+constexpr int AT_THREADS = 352;        // 8 softmax warps, 2 MMA issuers, 1 TMA producer
 constexpr uint32_t Q_BYTES = BQ * HD * 2;          // 16 KB per stream
 constexpr uint32_t K_BYTES = BK * HD * 2;          // 8 KB
 constexpr uint32_t V_BYTES = BK * HD * 2;          // 8 KB
@@ -78,7 +79,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_kv);
         mbar_init(q_full, 1);
-        for (int i = 0; i < KV_STAGES; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < KV_STAGES; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 2); }
         for (int i = 0; i < 4; i++) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -94,92 +95,74 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 9) {
+    if (warp == 10) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             mbar_expect_tx(q_full, 2 * Q_BYTES);
             tma_load_2d(smem_u32(smem + OFF_Q), &tm_q, smem_u32(q_full), h * HD, row0 + q0);
             tma_load_2d(smem_u32(smem + OFF_Q + Q_BYTES), &tm_q, smem_u32(q_full), h * HD, row0 + q0 + BQ);
+            int stage = 0;
+            uint32_t phase = 0;
             for (int t = 0; t < n_max; t++) {
-                const int stage = t % KV_STAGES;
-                const uint32_t phase = (uint32_t)(t / KV_STAGES) & 1u;
                 if (!mbar_wait(&kv_empty[stage], phase ^ 1u, abort_flag, err, 201)) break;
-                const uint32_t sk = smem_u32(smem + OFF_KV + stage * (K_BYTES + V_BYTES));
+                const uint32_t sk = smem_u32(smem + OFF_KV) + (uint32_t)stage * (K_BYTES + V_BYTES);
                 const uint32_t bar = smem_u32(&kv_full[stage]);
                 mbar_expect_tx(&kv_full[stage], K_BYTES + V_BYTES);
                 tma_load_2d(sk, &tm_kv, bar, d + h * HD, row0 + t * BK);
                 tma_load_2d(sk + K_BYTES, &tm_kv, bar, 2 * d + h * HD, row0 + t * BK);
+                if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer: one thread serves both streams
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ MMA issuers: one thread per stream
+        // Order per stream: S_0, S_1, then for every tile j: wait P_j -> O += P_j V_j -> give the key tile back ->
+        // S_{j+2}.  Both issuers wait on the same kv_full phases; a key tile returns to the producer after two
+        // arrivals on kv_empty, one per stream (a stream that does not need a tile arrives for it once it is loaded).
         if (lane == 0) {
+            const int s = warp - 8;
+            const int nt = s == 0 ? nt0 : nt1;
             bool ok = mbar_wait(q_full, 0, abort_flag, err, 202);
             tc_fence_after();
-            const int nt[2] = {nt0, nt1};
-            int s_issued[2] = {0, 0};       // S tiles issued per stream
-            int pv_issued[2] = {0, 0};      // P V products issued per stream
-            int kv_ready = 0;               // key tiles known to be in shared memory
-            int released = 0;               // key tiles handed back to the producer
-            unsigned long long idle_since = 0;
-            while (ok && (pv_issued[0] < nt[0] || pv_issued[1] < nt[1])) {
-                bool progress = false;
+            const uint64_t q_desc = make_smem_desc(smem_u32(smem + OFF_Q + s * Q_BYTES));
+            const uint64_t kv_desc0 = make_smem_desc(smem_u32(smem + OFF_KV));             // + stage * 1024 (16-byte units)
+            const uint64_t p_desc0 = make_smem_desc(smem_u32(smem + OFF_P + s * 2 * P_BYTES));
+            const uint32_t s_tmem0 = tmem_base + (uint32_t)(s * 128);
+            const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * HD);
+            constexpr uint64_t STAGE_UNITS = (K_BYTES + V_BYTES) >> 4, V_UNITS = K_BYTES >> 4, P_UNITS = P_BYTES >> 4;
+            int ld_stage = 0;            // stage / phase of the next tile whose S will be issued
+            uint32_t ld_phase = 0;
+            int use_stage = 0;           // stage of the next tile whose V will be consumed
+            auto issue_s = [&](int j) -> bool {
+                if (!mbar_wait(&kv_full[ld_stage], ld_phase, abort_flag, err, 203)) return false;
+                tc_fence_after();
+                const uint64_t k_desc = kv_desc0 + (uint64_t)ld_stage * STAGE_UNITS;
+                const uint32_t s_tmem = s_tmem0 + (uint32_t)((j & 1) * 64);
 #pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    // keep up to two score tiles ahead of the products
-                    while (ok && s_issued[s] < nt[s] && s_issued[s] < pv_issued[s] + 2) {
-                        const int j = s_issued[s];
-                        while (ok && kv_ready <= j) {
-                            if (!mbar_wait(&kv_full[kv_ready % KV_STAGES], (uint32_t)(kv_ready / KV_STAGES) & 1u, abort_flag, err, 203)) ok = false;
-                            else kv_ready++;
-                        }
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t sq = smem_u32(smem + OFF_Q + s * Q_BYTES);
-                        const uint32_t sk = smem_u32(smem + OFF_KV + (j % KV_STAGES) * (K_BYTES + V_BYTES));
-                        const uint32_t s_tmem = tmem_base + (uint32_t)(s * 128 + (j & 1) * 64);
+                for (int k = 0; k < HD / 16; k++) umma<false>(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0 ? 1u : 0u);
+                umma_commit(&s_full[s * 2 + (j & 1)]);
+                if (++ld_stage == KV_STAGES) { ld_stage = 0; ld_phase ^= 1u; }
+                return true;
+            };
+            if (ok && nt > 0) ok = issue_s(0);
+            if (ok && nt > 1) ok = issue_s(1);
+            for (int j = 0; j < nt && ok; j++) {
+                if (!mbar_wait(&p_full[s * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag, err, 204)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t p_desc = p_desc0 + (uint64_t)(j & 1) * P_UNITS;
+                const uint64_t v_desc = kv_desc0 + (uint64_t)use_stage * STAGE_UNITS + V_UNITS;
 #pragma unroll
-                        for (int k = 0; k < HD / 16; k++)
-                            umma<false>(s_tmem, make_smem_desc(sq + k * 32), make_smem_desc(sk + k * 32), IDESC_S, k != 0 ? 1u : 0u);
-                        umma_commit(&s_full[s * 2 + (j & 1)]);
-                        s_issued[s]++;
-                        progress = true;
-                    }
-                    if (ok && pv_issued[s] < nt[s]) {
-                        const int j = pv_issued[s];
-                        if (mbar_test_wait(&p_full[s * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u)) {
-                            tc_fence_after();
-                            const uint32_t sp = smem_u32(smem + OFF_P + (s * 2 + (j & 1)) * P_BYTES);
-                            const uint32_t sv = smem_u32(smem + OFF_KV + (j % KV_STAGES) * (K_BYTES + V_BYTES) + K_BYTES);
-                            const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * HD);
-#pragma unroll
-                            for (int kk = 0; kk < BK / 16; kk++)
-                                umma<false>(o_tmem, make_smem_desc(sp + kk * 32), make_smem_desc(sv + kk * 2048), IDESC_PV,
-                                            (j > 0 || kk != 0) ? 1u : 0u);
-                            umma_commit(&pv_done[s * 2 + (j & 1)]);
-                            pv_issued[s]++;
-                            progress = true;
-                            // a key tile goes back to the producer once every stream that needs it has used its V
-                            while (released < n_max && (released >= nt[0] || pv_issued[0] > released) &&
-                                   (released >= nt[1] || pv_issued[1] > released)) {
-                                umma_commit(&kv_empty[released % KV_STAGES]);
-                                released++;
-                            }
-                        }
-                    }
-                }
-                if (progress) {
-                    idle_since = 0;
-                } else {
-                    if (*abort_flag) { ok = false; break; }
-                    const unsigned long long now = globaltimer_ns();
-                    if (idle_since == 0) idle_since = now;
-                    else if (now - idle_since > WAIT_LIMIT_NS) {
-                        *abort_flag = 1;
-                        tl_dev_fail(err, TLNN_ERR_TIMEOUT, 204, (long long)blockIdx.x);
-                        ok = false;
-                    }
-                }
+                for (int kk = 0; kk < BK / 16; kk++)
+                    umma<false>(o_tmem, p_desc + 2 * kk, v_desc + 128 * kk, IDESC_PV, (j > 0 || kk != 0) ? 1u : 0u);
+                umma_commit(&pv_done[s * 2 + (j & 1)]);
+                umma_commit(&kv_empty[use_stage]);
+                if (++use_stage == KV_STAGES) use_stage = 0;
+                if (j + 2 < nt) ok = issue_s(j + 2);
+            }
+            // key tiles only the other stream needs: arrive for each once it is known to be loaded
+            for (int t = nt; t < n_max && ok; t++) {
+                if (!mbar_wait(&kv_full[ld_stage], ld_phase, abort_flag, err, 209)) { ok = false; break; }
+                mbar_arrive(&kv_empty[ld_stage]);
+                if (++ld_stage == KV_STAGES) { ld_stage = 0; ld_phase ^= 1u; }
             }
         }
     } else {
