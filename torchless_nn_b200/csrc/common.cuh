@@ -158,3 +158,9 @@ int tl_gemm_argmax_parts(int M, int N, int sm_count);
 // and head h at columns h*hd..(h+1)*hd inside each third.  out is (B, T, d) of the same kind.
 int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int out_kind,
                       int B, int T, int heads, int hd, int causal);
+
+// Copy the K and V thirds of a packed (B*T, 3d) projection into per-layer caches laid out (B, cache_len, d).
+int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int cache_len);
+int tl_run_block_kv(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
+                    int d, int heads, char* ws_base, void* kcache, void* vcache, int cache_len);
+size_t tl_block_ws_bytes(int prec, long long M, int d);

@@ -1,10 +1,375 @@
-// Greedy decode with a per-layer KV cache (placeholder until the cache kernels land).
+// Greedy decode with a per-layer KV cache.
+//
+// The reference generates by re-running the whole window for every new token (demo.ipynb:1526-1533).  Here the prompt
+// is run once (filling a (B, max_len, d) key and value cache per layer) and every further token costs one pass with a
+// single row per sequence: LayerNorm -> QKV GEMM -> append the row's K, V -> single-query attention over the cache ->
+// output GEMM + residual -> LayerNorm -> GEMM + activation -> GEMM + residual, then the final LayerNorm and the head
+// GEMM with fused arg-max.  The step is weight-streaming (HBM) bound.  The current length lives in device memory and
+// every kernel of a step reads it from there, so the launch sequence of a step does not depend on the position.
 #include "common.cuh"
 
-extern "C" int tlnn_decode_begin(tlnn_ctx*, const tlnn_gpt_model*, const void*, int, int, int, int, int32_t*, tlnn_decoder**) {
-    tl_set_error("decode is not built yet");
-    return TLNN_ERR_VALUE;
+namespace {
+
+constexpr int kWarp = 32;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;
+    u += 0x00000fffu + ((u >> 13) & 1u);
+    u &= 0xffffe000u;
+    return __uint_as_float(u);
 }
-extern "C" int tlnn_decode_step(tlnn_decoder*, const int32_t*, int32_t*) { tl_set_error("decode is not built yet"); return TLNN_ERR_VALUE; }
-extern "C" int tlnn_decode_run(tlnn_decoder*, const int32_t*, int, int32_t*) { tl_set_error("decode is not built yet"); return TLNN_ERR_VALUE; }
-extern "C" int tlnn_decode_end(tlnn_decoder*) { return TLNN_OK; }
+
+// qkv (B*T, 3d) -> kcache / vcache (B, cache_len, d), rows [0, T)
+template <typename E>
+__global__ void kv_store_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, int B, int T, int d,
+                                int cache_len) {
+    const long long total = (long long)B * T * d;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = (int)(i % d);
+        const long long row = i / d;
+        const int t = (int)(row % T);
+        const long long b = row / T;
+        const long long dst = (b * cache_len + t) * d + c;
+        kc[dst] = qkv[row * 3 * d + d + c];
+        vc[dst] = qkv[row * 3 * d + 2 * d + c];
+    }
+}
+
+// x[b, :] = table[token[b], :] + pos_table[*len, :]
+__global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const float* __restrict__ table,
+                                    const float* __restrict__ pos, const int* __restrict__ len, float* __restrict__ out,
+                                    int B, int d, int vocab, tlnn_dev_err* err) {
+    const int b = blockIdx.x;
+    long long id = tokens[b];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) tl_dev_fail(err, TLNN_ERR_INDEX, 2, id);
+        id = 0;
+    }
+    const int t = *len;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[(long long)b * d + c] = __fadd_rn(table[id * d + c], pos[(long long)t * d + c]);
+}
+
+// Append the new row's K, V (from the packed (B, 3d) projection) at position *len, then attend the row's query over
+// cache rows [0, *len].  One CTA per (sequence, head); keys are spread over the threads for the scores and the head
+// dimension over the threads for the weighted sum.
+template <typename E, int HD>
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, E* __restrict__ out,
+                        const int* __restrict__ len_ptr, int H, int cache_len, float inv_sqrt_hd, int round_out) {
+    extern __shared__ float sm[];
+    float* q = sm;                 // HD
+    float* sc = sm + HD;           // cache_len scores
+    __shared__ float red[8];
+    const int d = H * HD;
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const int pos = *len_ptr;
+    const int n = pos + 1;
+    const E* row = qkv + (long long)b * 3 * d;
+    E* kbase = kc + ((long long)b * cache_len) * d + h * HD;
+    E* vbase = vc + ((long long)b * cache_len) * d + h * HD;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < HD) {
+        q[tid] = to_f<E>(row[h * HD + tid]);
+        kbase[(long long)pos * d + tid] = row[d + h * HD + tid];
+        vbase[(long long)pos * d + tid] = row[2 * d + h * HD + tid];
+    }
+    __syncthreads();
+    // scores: one key per thread per pass (the new key is read back from the cache it was just written to)
+    float mx = -INFINITY;
+    for (int k = tid; k < n; k += 128) {
+        const E* kr = kbase + (long long)k * d;
+        float s = 0.f;
+#pragma unroll 8
+        for (int c = 0; c < HD; c++) s = fmaf(q[c], to_f<E>(kr[c]), s);
+        s *= inv_sqrt_hd;
+        sc[k] = s;
+        mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float sum = 0.f;
+    for (int k = tid; k < n; k += 128) {
+        const float p = expf(sc[k] - mx);
+        sc[k] = p;
+        sum += p;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[4 + warp] = sum;
+    __syncthreads();
+    sum = (red[4] + red[5]) + (red[6] + red[7]);
+    // weighted sum: thread -> (dimension, key residue); HD divides 128
+    constexpr int GROUPS = 128 / HD;
+    const int c = tid % HD, g = tid / HD;
+    float acc = 0.f;
+    for (int k = g; k < n; k += GROUPS) acc = fmaf(sc[k], to_f<E>(vbase[(long long)k * d + c]), acc);
+    if (GROUPS > 1) {
+        __shared__ float partial[128];
+        partial[tid] = acc;
+        __syncthreads();
+        if (g == 0) {
+#pragma unroll
+            for (int j = 1; j < GROUPS; j++) acc += partial[j * HD + c];
+        }
+    }
+    if (g == 0) {
+        float o = acc / sum;
+        if (round_out) o = round_tf32(o);
+        out[(long long)b * d + h * HD + c] = from_f<E>(o);
+    }
+}
+
+// tokens_out[b, *step] = next[b]; then advance the position and the step counter
+__global__ void decode_advance_kernel(const int32_t* __restrict__ next, int32_t* __restrict__ cur, int32_t* tokens_out,
+                                      int n_cols, int* len, int* step, int B) {
+    const int s = *step;
+    __syncthreads();
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const int32_t t = next[b];
+        cur[b] = t;
+        if (tokens_out) tokens_out[(long long)b * n_cols + s] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { *len += 1; *step = s + 1; }
+}
+
+inline size_t esize(int prec) { return prec == TLNN_PREC_BF16 ? 2 : 4; }
+inline int okind(int prec) { return prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_TF32; }
+
+}  // namespace
+
+int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int cache_len) {
+    const size_t n = (size_t)B * T * d;
+    if (n == 0) return TLNN_OK;
+    int grid = (int)((n + 255) / 256);
+    if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
+    if (prec == TLNN_PREC_BF16)
+        TL_LAUNCH(ctx, "kv_store", kv_store_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>(
+                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, B, T, d, cache_len));
+    else
+        TL_LAUNCH(ctx, "kv_store", kv_store_kernel<float><<<grid, 256, 0, ctx->stream>>>(
+                      (const float*)qkv, (float*)kcache, (float*)vcache, B, T, d, cache_len));
+    return TLNN_OK;
+}
+
+struct tlnn_decoder {
+    tlnn_ctx* ctx = nullptr;
+    tlnn_gpt_model m;                            // copy of the description (pointers stay owned by the caller)
+    std::vector<tlnn_block_params> blocks;
+    int B = 0, max_len = 0, host_len = 0;
+    char* mem = nullptr;                         // one allocation for caches and per-step buffers
+    void *kcache = nullptr, *vcache = nullptr;   // (layers, B, max_len, d)
+    float *x0 = nullptr, *x1 = nullptr, *y = nullptr;
+    void *a = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr;
+    float2* parts = nullptr;
+    int32_t *cur = nullptr, *next = nullptr;
+    int *d_len = nullptr, *d_step = nullptr;
+    int n_parts = 0;
+};
+
+namespace {
+
+int launch_decode_attention(tlnn_decoder* dec, int layer) {
+    tlnn_ctx* ctx = dec->ctx;
+    const int d = dec->m.d, H = dec->m.heads, hd = d / H, B = dec->B;
+    const size_t layer_elems = (size_t)B * dec->max_len * d;
+    const float inv = 1.f / sqrtf((float)hd);
+    const size_t smem = (size_t)(hd + dec->max_len) * sizeof(float);
+    const int round_out = dec->m.prec == TLNN_PREC_TF32;
+#define DA_CASE(E, HDV)                                                                                              \
+    TL_LAUNCH(ctx, "decode_attention", decode_attention_kernel<E, HDV><<<B * H, 128, smem, ctx->stream>>>(           \
+                  (const E*)dec->qkv, (E*)dec->kcache + layer * layer_elems, (E*)dec->vcache + layer * layer_elems, \
+                  (E*)dec->att, dec->d_len, H, dec->max_len, inv, round_out))
+    if (dec->m.prec == TLNN_PREC_BF16) {
+        if (hd == 32) DA_CASE(__nv_bfloat16, 32);
+        else if (hd == 64) DA_CASE(__nv_bfloat16, 64);
+        else DA_CASE(__nv_bfloat16, 128);
+    } else {
+        if (hd == 32) DA_CASE(float, 32);
+        else if (hd == 64) DA_CASE(float, 64);
+        else DA_CASE(float, 128);
+    }
+#undef DA_CASE
+    return TLNN_OK;
+}
+
+// One token for every sequence: cur tokens at position *d_len -> next tokens; advances the device counters.
+int decode_one(tlnn_decoder* dec, int32_t* tokens_out, int n_cols) {
+    tlnn_ctx* ctx = dec->ctx;
+    const tlnn_gpt_model& m = dec->m;
+    const int B = dec->B, d = m.d, prec = m.prec, kind = okind(prec);
+    TL_LAUNCH(ctx, "decode_embed", decode_embed_kernel<<<B, 128, 0, ctx->stream>>>(dec->cur, m.tok_table, m.pos_table,
+                                                                                   dec->d_len, dec->x0, B, d, m.vocab, ctx->d_err));
+    float* x = dec->x0;
+    float* xn = dec->x1;
+    for (int l = 0; l < m.layers; l++) {
+        const tlnn_block_params& p = dec->blocks[l];
+        TL_TRY(tl_layernorm(ctx, x, p.ln1_gamma, p.ln1_beta, 1e-5f, dec->a, kind, B, d));
+        tl_gemm_epilogue e1;
+        e1.bias = p.bqkv; e1.out = dec->qkv; e1.ldo = 3 * d; e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_F32;
+        TL_TRY(tl_gemm(ctx, prec, dec->a, d, p.wqkv_t, d, B, 3 * d, d, e1));
+        TL_TRY(launch_decode_attention(dec, l));
+        tl_gemm_epilogue e2;
+        e2.bias = p.bo; e2.residual = x; e2.ldr = d; e2.out = dec->y; e2.ldo = d; e2.out_kind = TL_OUT_F32;
+        TL_TRY(tl_gemm(ctx, prec, dec->att, d, p.wo_t, d, B, d, d, e2));
+        TL_TRY(tl_layernorm(ctx, dec->y, p.ln2_gamma, p.ln2_beta, 1e-5f, dec->a, kind, B, d));
+        tl_gemm_epilogue e3;
+        e3.bias = p.b1; e3.act = m.act; e3.accurate_math = prec == TLNN_PREC_TF32; e3.out = dec->hid; e3.ldo = 4 * d; e3.out_kind = kind;
+        TL_TRY(tl_gemm(ctx, prec, dec->a, d, p.w1_t, d, B, 4 * d, d, e3));
+        tl_gemm_epilogue e4;
+        e4.bias = p.b2; e4.residual = dec->y; e4.ldr = d; e4.out = xn; e4.ldo = d; e4.out_kind = TL_OUT_F32;
+        TL_TRY(tl_gemm(ctx, prec, dec->hid, 4 * d, p.w2_t, 4 * d, B, d, 4 * d, e4));
+        float* t = x; x = xn; xn = t;
+    }
+    TL_TRY(tl_layernorm(ctx, x, m.lnf_gamma, m.lnf_beta, 1e-5f, dec->a, kind, B, d));
+    tl_gemm_epilogue eh;
+    eh.bias = m.head_bias; eh.argmax_partials = dec->parts;
+    TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
+    TL_TRY(tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B));
+    TL_LAUNCH(ctx, "decode_advance", decode_advance_kernel<<<1, 256, 0, ctx->stream>>>(dec->next, dec->cur, tokens_out, n_cols,
+                                                                                      dec->d_len, dec->d_step, B));
+    dec->host_len++;
+    return TLNN_OK;
+}
+
+}  // namespace
+
+extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T0,
+                                 int max_len, int32_t* first_tokens, tlnn_decoder** out) {
+    TL_NOTNULL(ctx); TL_NOTNULL(m); TL_NOTNULL(ids); TL_NOTNULL(first_tokens); TL_NOTNULL(out);
+    TL_NOTNULL(m->tok_table); TL_NOTNULL(m->pos_table); TL_NOTNULL(m->lnf_gamma); TL_NOTNULL(m->lnf_beta); TL_NOTNULL(m->head_t);
+    TL_REQUIRE(m->layers == 0 || m->blocks != nullptr, "decode: the model has layers but no block parameters");
+    TL_REQUIRE(m->prec == TLNN_PREC_BF16 || m->prec == TLNN_PREC_TF32, "unknown precision %d", m->prec);
+    TL_REQUIRE(B > 0 && B <= 1024 && T0 > 0, "decode: bad batch %d or prompt length %d", B, T0);
+    TL_REQUIRE(max_len > T0 && max_len <= m->context, "decode: prompt %d + new tokens must fit max_len %d <= context %d", T0, max_len, m->context);
+    TL_REQUIRE(m->d > 0 && m->heads > 0 && m->d % m->heads == 0 && m->d % 8 == 0, "decode: bad width %d / heads %d", m->d, m->heads);
+    const int hd = m->d / m->heads;
+    TL_REQUIRE(hd == 32 || hd == 64 || hd == 128, "decode: head dimension %d is not supported (32, 64 or 128)", hd);
+    TL_REQUIRE((long long)B * m->heads <= 65535, "decode: batch x heads exceeds 65535");
+    TL_REQUIRE(ids_type == TLNN_I32 || ids_type == TLNN_I64 || ids_type == TLNN_U8, "token ids must be int32, int64 or uint8");
+    TL_CUDA(cudaSetDevice(ctx->device));
+
+    tlnn_decoder* dec = new tlnn_decoder();
+    dec->ctx = ctx;
+    dec->m = *m;
+    dec->blocks.assign(m->blocks, m->blocks + m->layers);
+    dec->m.blocks = dec->blocks.data();
+    dec->B = B;
+    dec->max_len = max_len;
+    const int d = m->d, prec = m->prec;
+    const size_t es = esize(prec);
+    dec->n_parts = tl_gemm_argmax_parts(B, m->vocab, ctx->sm_count);
+    // carve one allocation
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
+    const size_t cache_bytes = (size_t)m->layers * B * max_len * d * es;
+    const size_t o_k = take(cache_bytes), o_v = take(cache_bytes);
+    const size_t o_x0 = take((size_t)B * d * 4), o_x1 = take((size_t)B * d * 4), o_y = take((size_t)B * d * 4);
+    const size_t o_a = take((size_t)B * d * es), o_qkv = take((size_t)B * 3 * d * es), o_att = take((size_t)B * d * es);
+    const size_t o_hid = take((size_t)B * 4 * d * es), o_parts = take((size_t)B * dec->n_parts * sizeof(float2));
+    const size_t o_cur = take((size_t)B * 4), o_next = take((size_t)B * 4), o_cnt = take(16);
+    cudaError_t e = cudaMalloc(&dec->mem, off);
+    if (e != cudaSuccess) { delete dec; return tl_cuda_fail(e, "cudaMalloc(decoder)", __FILE__, __LINE__); }
+    char* base = dec->mem;
+    dec->kcache = base + o_k; dec->vcache = base + o_v;
+    dec->x0 = (float*)(base + o_x0); dec->x1 = (float*)(base + o_x1); dec->y = (float*)(base + o_y);
+    dec->a = base + o_a; dec->qkv = base + o_qkv; dec->att = base + o_att; dec->hid = base + o_hid;
+    dec->parts = (float2*)(base + o_parts);
+    dec->cur = (int32_t*)(base + o_cur); dec->next = (int32_t*)(base + o_next);
+    dec->d_len = (int*)(base + o_cnt); dec->d_step = dec->d_len + 1;
+
+    // ---- prompt: the blocks of the prefill path, also filling the caches
+    int status = TLNN_OK;
+    do {
+        const long long M = (long long)B * T0;
+        const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
+        const size_t head_bytes = tl_ws_round((size_t)B * d * 4);
+        status = tl_ws_reserve(ctx, 2 * stream_bytes + tl_block_ws_bytes(prec, M, d) + head_bytes);
+        if (status) break;
+        float* xa = (float*)ctx->ws;
+        float* xb = (float*)(ctx->ws + stream_bytes);
+        char* tail = ctx->ws + 2 * stream_bytes;
+        status = tl_embed(ctx, ids, ids_type, m->tok_table, m->pos_table, xa, B, T0, d, m->vocab);
+        if (status) break;
+        const size_t layer_bytes = (size_t)B * max_len * d * es;
+        for (int l = 0; l < m->layers && !status; l++) {
+            status = tl_run_block_kv(ctx, prec, xa, &dec->blocks[l], m->act, xb, B, T0, d, m->heads, tail,
+                                     (char*)dec->kcache + l * layer_bytes, (char*)dec->vcache + l * layer_bytes, max_len);
+            float* t = xa; xa = xb; xb = t;
+        }
+        if (status) break;
+        // last position of every prompt -> final LayerNorm -> head with arg-max
+        float* last = (float*)(tail + tl_block_ws_bytes(prec, M, d));
+        status = tl_convert(ctx, xa + (size_t)(T0 - 1) * d, (long long)T0 * d, last, TL_OUT_F32, B, d);
+        if (status) break;
+        status = tl_layernorm(ctx, last, m->lnf_gamma, m->lnf_beta, 1e-5f, dec->a, okind(prec), B, d);
+        if (status) break;
+        tl_gemm_epilogue eh;
+        eh.bias = m->head_bias; eh.argmax_partials = dec->parts;
+        status = tl_gemm(ctx, prec, dec->a, d, m->head_t, d, B, m->vocab, d, eh);
+        if (status) break;
+        status = tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B);
+        if (status) break;
+        int init[2] = {T0, 0};
+        cudaError_t ce = cudaMemcpyAsync(dec->d_len, init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream);
+        if (ce == cudaSuccess) ce = cudaMemcpyAsync(first_tokens, dec->next, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (ce == cudaSuccess) ce = cudaMemcpyAsync(dec->cur, dec->next, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx->stream);      // `init` is a stack array
+        if (ce != cudaSuccess) status = tl_cuda_fail(ce, "decode_begin copies", __FILE__, __LINE__);
+        dec->host_len = T0;
+    } while (0);
+    if (status) {
+        cudaFree(dec->mem);
+        delete dec;
+        return status;
+    }
+    *out = dec;
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_decode_step(tlnn_decoder* dec, const int32_t* prev_tokens, int32_t* next_tokens) {
+    TL_NOTNULL(dec); TL_NOTNULL(prev_tokens); TL_NOTNULL(next_tokens);
+    tlnn_ctx* ctx = dec->ctx;
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_REQUIRE(dec->host_len < dec->max_len, "decode: the cache is full (%d positions)", dec->max_len);
+    if (prev_tokens != dec->cur)
+        TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_TRY(decode_one(dec, nullptr, 0));
+    TL_CUDA(cudaMemcpyAsync(next_tokens, dec->next, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_decode_run(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, int32_t* tokens_out) {
+    TL_NOTNULL(dec); TL_NOTNULL(prev_tokens); TL_NOTNULL(tokens_out);
+    tlnn_ctx* ctx = dec->ctx;
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_REQUIRE(n_steps >= 0 && dec->host_len + n_steps <= dec->max_len, "decode: %d steps do not fit the cache (%d of %d used)",
+               n_steps, dec->host_len, dec->max_len);
+    if (n_steps == 0) return TLNN_OK;
+    if (prev_tokens != dec->cur)
+        TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_CUDA(cudaMemsetAsync(dec->d_step, 0, sizeof(int), ctx->stream));
+    for (int s = 0; s < n_steps; s++) TL_TRY(decode_one(dec, tokens_out, n_steps));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_decode_end(tlnn_decoder* dec) {
+    if (!dec) return TLNN_OK;
+    cudaSetDevice(dec->ctx->device);
+    cudaStreamSynchronize(dec->ctx->stream);
+    cudaFree(dec->mem);
+    delete dec;
+    return TLNN_OK;
+}

@@ -427,7 +427,7 @@ int pick_bn(int M, int N, int sm_count) {
     const int m_tiles = (M + BM - 1) / BM;
     if (N > 128 && (long long)m_tiles * ((N + 255) / 256) >= sm_count) return 256;
     if (N > 64 && (long long)m_tiles * ((N + 127) / 128) >= sm_count) return 128;
-    if (N > 128) return 128;
+    // too few tiles to fill the SMs either way: the narrowest tile gives the most CTAs streaming the weight
     return 64;
 }
 

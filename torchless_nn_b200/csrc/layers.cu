@@ -56,7 +56,8 @@ size_t block_ws_bytes(int prec, long long M, int d) {
 
 // One pre-LN block on rows already resident in float32.  `cur` is advanced past the pieces taken.
 int run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
-              int d, int heads, int causal, tl_ws_cursor cur) {
+              int d, int heads, int causal, tl_ws_cursor cur, void* kcache = nullptr, void* vcache = nullptr,
+              int cache_len = 0) {
     const long long M = (long long)B * T;
     const int kind = op_kind(prec);
     const int accurate = prec == TLNN_PREC_TF32;
@@ -71,6 +72,7 @@ int run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* 
     e1.bias = p->bqkv; e1.out = qkv; e1.ldo = 3 * d;
     e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_F32;    // float32 attention reads unrounded q, k, v
     TL_TRY(tl_gemm(ctx, prec, a, d, p->wqkv_t, d, (int)M, 3 * d, d, e1));
+    if (kcache) TL_TRY(tl_kv_store(ctx, prec, qkv, kcache, vcache, B, T, d, cache_len));
     TL_TRY(tl_attention_core(ctx, prec, qkv, att, kind, B, T, heads, d / heads, causal));
     tl_gemm_epilogue e2;
     e2.bias = p->bo; e2.residual = x; e2.ldr = d; e2.out = y; e2.ldo = d; e2.out_kind = TL_OUT_F32;
@@ -117,12 +119,13 @@ int run_head(tlnn_ctx* ctx, int prec, const void* a, const void* table_t, const 
 
 }  // namespace
 
-// Shared with the decode path.
-int tl_run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
-                 int d, int heads, int causal, char* ws_base) {
+// Shared with the decode path: one causal block over a prompt, also copying the block's keys and values into the
+// layer's cache (rows [0, T) of every sequence; the cache holds cache_len rows per sequence).
+int tl_run_block_kv(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
+                    int d, int heads, char* ws_base, void* kcache, void* vcache, int cache_len) {
     tl_ws_cursor cur(ctx);
     cur.base = ws_base;
-    return run_block(ctx, prec, x, p, act, out, B, T, d, heads, causal, cur);
+    return run_block(ctx, prec, x, p, act, out, B, T, d, heads, 1, cur, kcache, vcache, cache_len);
 }
 size_t tl_block_ws_bytes(int prec, long long M, int d) { return block_ws_bytes(prec, M, d); }
 
