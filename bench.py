@@ -367,18 +367,77 @@ def run_b200(args, spec):
     return 0
 
 
+def run_other(args, spec):
+    """Secondary configurations (single GPU): c2 ViT images/s, c4 greedy decode tokens/s.  Same JSON skeleton; these
+    lines document the other configurations and are not the headline metric."""
+    import ctypes as C
+    from torchless_nn_b200 import backend, _lib
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.models import build_network, load_params
+    backend.set_precision(spec.precision)
+    ctx = backend.ctx()
+    net = build_network(spec)
+    load_params(net, wl.seeded_params(spec))
+    x = wl.make_inputs(spec)
+    ms = C.c_float()
+    if spec.kind == "vit":
+        from torchless_nn_b200.backend import xp
+        xd = xp.array(x)
+        step = lambda: xp.argmax(net.predict(xd))
+        units, metric, unit = spec.batch, "vit_forward_images_per_s", "images/s"
+        flops = spec.flops_per_image() * spec.batch
+    else:
+        step = lambda: net.generate_greedy(x, wl.C4_NEW_TOKENS)
+        units, metric, unit = spec.batch * wl.C4_NEW_TOKENS, "gpt_greedy_decode_new_tokens_per_s", "tokens/s"
+        flops = None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    backend.synchronize()
+    backend.launch_count(reset=True)
+    check(lib.tlnn_prof_begin(ctx))
+    for _ in range(args.steps):
+        step()
+    check(lib.tlnn_prof_end(ctx, C.byref(ms)))
+    launches = backend.launch_count()
+    # a second, untimed pass with per-launch events for the per-kernel breakdown (it serialises launches)
+    check(lib.tlnn_prof_classes(ctx, 1))
+    step()
+    rows = (_lib.ProfRow * 64)()
+    n_rows = lib.tlnn_prof_table(ctx, rows, 64)
+    check(lib.tlnn_prof_classes(ctx, 0))
+    classes = {r.name.decode(): round(float(r.ms), 4) for r in rows[:n_rows]}
+    line = {"metric": metric, "value": units * args.steps / (ms.value * 1e-3), "unit": unit, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms.value / args.steps, "higher_is_better": True,
+            "dtype": "bf16" if spec.precision == "bf16" else "tf32", "data": "synthetic",
+            "config": {"workload": spec.name}, "gpu_launches": int(launches), "kernel_classes_ms_per_step": classes}
+    if flops:
+        line["tflops"] = flops * args.steps / (ms.value * 1e-3) / 1e12
+    if spec.kind == "gpt":
+        # decode is weight- and cache-streaming bound: bytes = weights once per step + K/V read per step
+        d, L = spec.d_model, spec.layers
+        w_bytes = 2.0 * (spec.n_params() - spec.context * d)          # bf16, tied table doubles as the head
+        kv = sum(2.0 * spec.batch * L * (spec.seq_len + i) * d * 2 for i in range(wl.C4_NEW_TOKENS))
+        total = w_bytes * wl.C4_NEW_TOKENS + kv
+        line["hbm_bytes_per_run"] = total
+        line["hbm_gbs_achieved_incl_prefill_time"] = total * args.steps / (ms.value * 1e-3) / 1e9
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="c5", choices=["c5", "c3"])
+    ap.add_argument("--config", default="c5", choices=["c5", "c3", "c1", "c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     spec = wl.CONFIGS[args.config]
     if args.impl == "reference":
         return run_reference(args, spec)
+    if args.config in ("c2", "c4"):
+        return run_other(args, spec)
     return run_b200(args, spec)
 
 

@@ -88,8 +88,14 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
     for (int k = tid; k < n; k += 128) {
         const E* kr = kbase + (long long)k * d;
         float s = 0.f;
-#pragma unroll 8
-        for (int c = 0; c < HD; c++) s = fmaf(q[c], to_f<E>(kr[c]), s);
+        constexpr int PER = 16 / sizeof(E);          // elements per 16-byte load (rows are 16-byte aligned)
+#pragma unroll
+        for (int c = 0; c < HD; c += PER) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+            const E* e = reinterpret_cast<const E*>(&raw);
+#pragma unroll
+            for (int i = 0; i < PER; i++) s = fmaf(q[c + i], to_f<E>(e[i]), s);
+        }
         s *= inv_sqrt_hd;
         sc[k] = s;
         mx = fmaxf(mx, s);
@@ -132,9 +138,17 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
 }
 
 // tokens_out[b, *step] = next[b]; then advance the position and the step counter
-__global__ void decode_advance_kernel(const int32_t* __restrict__ next, int32_t* __restrict__ cur, int32_t* tokens_out,
-                                      int n_cols, int* len, int* step, int B) {
+struct decode_sink {          // lives in device memory so that a captured step does not depend on call arguments
+    int32_t* tokens_out;      // (B, n_cols) or null
+    int n_cols;
+    int pad;
+};
+
+__global__ void decode_advance_kernel(const int32_t* __restrict__ next, int32_t* __restrict__ cur,
+                                      const decode_sink* __restrict__ sink, int* len, int* step, int B) {
     const int s = *step;
+    int32_t* tokens_out = sink->tokens_out;
+    const int n_cols = sink->n_cols;
     __syncthreads();
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         const int32_t t = next[b];
@@ -176,7 +190,10 @@ struct tlnn_decoder {
     float2* parts = nullptr;
     int32_t *cur = nullptr, *next = nullptr;
     int *d_len = nullptr, *d_step = nullptr;
+    decode_sink* d_sink = nullptr;
     int n_parts = 0;
+    cudaGraphExec_t step_graph = nullptr;        // one captured step, replayed by tlnn_decode_run
+    long long launches_per_step = 0;
 };
 
 namespace {
@@ -206,7 +223,7 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
 }
 
 // One token for every sequence: cur tokens at position *d_len -> next tokens; advances the device counters.
-int decode_one(tlnn_decoder* dec, int32_t* tokens_out, int n_cols) {
+int decode_one(tlnn_decoder* dec) {
     tlnn_ctx* ctx = dec->ctx;
     const tlnn_gpt_model& m = dec->m;
     const int B = dec->B, d = m.d, prec = m.prec, kind = okind(prec);
@@ -238,9 +255,17 @@ int decode_one(tlnn_decoder* dec, int32_t* tokens_out, int n_cols) {
     eh.bias = m.head_bias; eh.argmax_partials = dec->parts;
     TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
     TL_TRY(tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B));
-    TL_LAUNCH(ctx, "decode_advance", decode_advance_kernel<<<1, 256, 0, ctx->stream>>>(dec->next, dec->cur, tokens_out, n_cols,
+    TL_LAUNCH(ctx, "decode_advance", decode_advance_kernel<<<1, 256, 0, ctx->stream>>>(dec->next, dec->cur, dec->d_sink,
                                                                                       dec->d_len, dec->d_step, B));
-    dec->host_len++;
+    return TLNN_OK;
+}
+
+int set_sink(tlnn_decoder* dec, int32_t* tokens_out, int n_cols) {
+    decode_sink h;
+    h.tokens_out = tokens_out; h.n_cols = n_cols; h.pad = 0;
+    // a synchronous copy from a stack object; the stream is idle or ordered behind it either way
+    TL_CUDA(cudaMemcpyAsync(dec->d_sink, &h, sizeof(h), cudaMemcpyHostToDevice, dec->ctx->stream));
+    TL_CUDA(cudaStreamSynchronize(dec->ctx->stream));
     return TLNN_OK;
 }
 
@@ -279,7 +304,7 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     const size_t o_x0 = take((size_t)B * d * 4), o_x1 = take((size_t)B * d * 4), o_y = take((size_t)B * d * 4);
     const size_t o_a = take((size_t)B * d * es), o_qkv = take((size_t)B * 3 * d * es), o_att = take((size_t)B * d * es);
     const size_t o_hid = take((size_t)B * 4 * d * es), o_parts = take((size_t)B * dec->n_parts * sizeof(float2));
-    const size_t o_cur = take((size_t)B * 4), o_next = take((size_t)B * 4), o_cnt = take(16);
+    const size_t o_cur = take((size_t)B * 4), o_next = take((size_t)B * 4), o_cnt = take(16), o_sink = take(sizeof(decode_sink));
     cudaError_t e = cudaMalloc(&dec->mem, off);
     if (e != cudaSuccess) { delete dec; return tl_cuda_fail(e, "cudaMalloc(decoder)", __FILE__, __LINE__); }
     char* base = dec->mem;
@@ -289,6 +314,7 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     dec->parts = (float2*)(base + o_parts);
     dec->cur = (int32_t*)(base + o_cur); dec->next = (int32_t*)(base + o_next);
     dec->d_len = (int*)(base + o_cnt); dec->d_step = dec->d_len + 1;
+    dec->d_sink = (decode_sink*)(base + o_sink);
 
     // ---- prompt: the blocks of the prefill path, also filling the caches
     int status = TLNN_OK;
@@ -346,7 +372,9 @@ extern "C" int tlnn_decode_step(tlnn_decoder* dec, const int32_t* prev_tokens, i
     TL_REQUIRE(dec->host_len < dec->max_len, "decode: the cache is full (%d positions)", dec->max_len);
     if (prev_tokens != dec->cur)
         TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    TL_TRY(decode_one(dec, nullptr, 0));
+    TL_TRY(set_sink(dec, nullptr, 0));
+    TL_TRY(decode_one(dec));
+    dec->host_len++;
     TL_CUDA(cudaMemcpyAsync(next_tokens, dec->next, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return TLNN_OK;
 }
@@ -360,8 +388,33 @@ extern "C" int tlnn_decode_run(tlnn_decoder* dec, const int32_t* prev_tokens, in
     if (n_steps == 0) return TLNN_OK;
     if (prev_tokens != dec->cur)
         TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_TRY(set_sink(dec, tokens_out, n_steps));
     TL_CUDA(cudaMemsetAsync(dec->d_step, 0, sizeof(int), ctx->stream));
-    for (int s = 0; s < n_steps; s++) TL_TRY(decode_one(dec, tokens_out, n_steps));
+    // Every kernel of a step takes the position from device memory, so one step is captured once as a CUDA graph and
+    // replayed; per-launch timing (tlnn_prof_classes) needs plain launches and bypasses the graph.
+    if (!ctx->prof_classes && !dec->step_graph) {
+        cudaGraph_t graph = nullptr;
+        const long long before = ctx->launches;
+        TL_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const int st = decode_one(dec);
+        dec->launches_per_step = ctx->launches - before;
+        ctx->launches = before;                  // capturing records launches without running them
+        const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+        if (st != TLNN_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (ce != cudaSuccess) return tl_cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
+        const cudaError_t ie = cudaGraphInstantiate(&dec->step_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) return tl_cuda_fail(ie, "cudaGraphInstantiate", __FILE__, __LINE__);
+    }
+    for (int s = 0; s < n_steps; s++) {
+        if (dec->step_graph && !ctx->prof_classes) {
+            TL_CUDA(cudaGraphLaunch(dec->step_graph, ctx->stream));
+            ctx->launches += dec->launches_per_step;
+        } else {
+            TL_TRY(decode_one(dec));
+        }
+        dec->host_len++;
+    }
     return TLNN_OK;
 }
 
@@ -369,6 +422,7 @@ extern "C" int tlnn_decode_end(tlnn_decoder* dec) {
     if (!dec) return TLNN_OK;
     cudaSetDevice(dec->ctx->device);
     cudaStreamSynchronize(dec->ctx->stream);
+    if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
     cudaFree(dec->mem);
     delete dec;
     return TLNN_OK;
