@@ -387,8 +387,8 @@ def run_other(args, spec):
         units, metric, unit = spec.batch, "vit_forward_images_per_s", "images/s"
         flops = spec.flops_per_image() * spec.batch
     else:
-        step = lambda: net.generate_greedy(x, wl.C4_NEW_TOKENS)
-        units, metric, unit = spec.batch * wl.C4_NEW_TOKENS, "gpt_greedy_decode_new_tokens_per_s", "tokens/s"
+        step = lambda: net.generate_greedy(x, args.new_tokens)
+        units, metric, unit = spec.batch * args.new_tokens, "gpt_greedy_decode_new_tokens_per_s", "tokens/s"
         flops = None
     for _ in range(max(args.warmup, 3)):
         step()
@@ -416,8 +416,8 @@ def run_other(args, spec):
         # decode is weight- and cache-streaming bound: bytes = weights once per step + K/V read per step
         d, L = spec.d_model, spec.layers
         w_bytes = 2.0 * (spec.n_params() - spec.context * d)          # bf16, tied table doubles as the head
-        kv = sum(2.0 * spec.batch * L * (spec.seq_len + i) * d * 2 for i in range(wl.C4_NEW_TOKENS))
-        total = w_bytes * wl.C4_NEW_TOKENS + kv
+        kv = sum(2.0 * spec.batch * L * (spec.seq_len + i) * d * 2 for i in range(args.new_tokens))
+        total = w_bytes * args.new_tokens + kv
         line["hbm_bytes_per_run"] = total
         line["hbm_gbs_achieved_incl_prefill_time"] = total * args.steps / (ms.value * 1e-3) / 1e9
     print(json.dumps(line), flush=True)
@@ -432,6 +432,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c5", choices=["c5", "c3", "c1", "c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--new-tokens", type=int, default=wl.C4_NEW_TOKENS, help="c4 only: tokens generated per prompt")
     args = ap.parse_args()
     spec = wl.CONFIGS[args.config]
     if args.impl == "reference":

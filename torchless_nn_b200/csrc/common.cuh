@@ -45,6 +45,7 @@ struct tlnn_ctx {
     // grow-only scratch arena used by the composite layer calls (stream-ordered reuse)
     char* ws = nullptr;
     size_t ws_bytes = 0;
+
     // whole-interval timing
     cudaEvent_t prof_a = nullptr, prof_b = nullptr;
     // per-class timing
@@ -164,3 +165,4 @@ int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vc
 int tl_run_block_kv(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
                     int d, int heads, char* ws_base, void* kcache, void* vcache, int cache_len);
 size_t tl_block_ws_bytes(int prec, long long M, int d);
+

@@ -59,16 +59,20 @@ __global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const fl
 }
 
 // Append the new row's K, V (from the packed (B, 3d) projection) at position *len, then attend the row's query over
-// cache rows [0, *len].  One CTA per (sequence, head); keys are spread over the threads for the scores and the head
-// dimension over the threads for the weighted sum.
+// cache rows [0, *len].  One CTA per (sequence, head).  Both passes read the cache with 16-byte loads: a group of
+// HD*sizeof(E)/16 threads covers one key row, and the 128 threads cover 128 / group keys per pass, so every pass keeps
+// many independent loads in flight.
 template <typename E, int HD>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, E* __restrict__ out,
                         const int* __restrict__ len_ptr, int H, int cache_len, float inv_sqrt_hd, int round_out) {
+    constexpr int PER = 16 / sizeof(E);            // elements per 16-byte load
+    constexpr int TPR = HD / PER;                  // threads per key row
+    constexpr int KPP = 128 / TPR;                 // keys per pass
     extern __shared__ float sm[];
-    float* q = sm;                 // HD
-    float* sc = sm + HD;           // cache_len scores
+    float* sc = sm;                                // cache_len scores / probabilities
     __shared__ float red[8];
+    __shared__ float part[128 * PER];              // KPP x HD partial outputs
     const int d = H * HD;
     const int b = blockIdx.x / H, h = blockIdx.x % H;
     const int pos = *len_ptr;
@@ -77,28 +81,38 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
     E* kbase = kc + ((long long)b * cache_len) * d + h * HD;
     E* vbase = vc + ((long long)b * cache_len) * d + h * HD;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid < HD) {
-        q[tid] = to_f<E>(row[h * HD + tid]);
-        kbase[(long long)pos * d + tid] = row[d + h * HD + tid];
-        vbase[(long long)pos * d + tid] = row[2 * d + h * HD + tid];
+    const int sub = tid % TPR, grp = tid / TPR;    // 16-byte unit inside the row, key residue
+    // this thread's slice of the query, and the append of the new row (first TPR threads, 16 bytes each)
+    float q[PER];
+    {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + h * HD + sub * PER);
+        const E* e = reinterpret_cast<const E*>(&raw);
+#pragma unroll
+        for (int i = 0; i < PER; i++) q[i] = to_f<E>(e[i]);
+        if (grp == 0) {
+            *reinterpret_cast<uint4*>(kbase + (long long)pos * d + sub * PER) = *reinterpret_cast<const uint4*>(row + d + h * HD + sub * PER);
+            *reinterpret_cast<uint4*>(vbase + (long long)pos * d + sub * PER) = *reinterpret_cast<const uint4*>(row + 2 * d + h * HD + sub * PER);
+        }
     }
     __syncthreads();
-    // scores: one key per thread per pass (the new key is read back from the cache it was just written to)
+    // scores: TPR threads per key, partial dot products combined by shuffles inside the group
     float mx = -INFINITY;
-    for (int k = tid; k < n; k += 128) {
-        const E* kr = kbase + (long long)k * d;
+    for (int k0 = 0; k0 < n; k0 += KPP) {
+        const int k = k0 + grp;
         float s = 0.f;
-        constexpr int PER = 16 / sizeof(E);          // elements per 16-byte load (rows are 16-byte aligned)
-#pragma unroll
-        for (int c = 0; c < HD; c += PER) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+        if (k < n) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(kbase + (long long)k * d + sub * PER);
             const E* e = reinterpret_cast<const E*>(&raw);
 #pragma unroll
-            for (int i = 0; i < PER; i++) s = fmaf(q[c + i], to_f<E>(e[i]), s);
+            for (int i = 0; i < PER; i++) s = fmaf(q[i], to_f<E>(e[i]), s);
         }
+#pragma unroll
+        for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         s *= inv_sqrt_hd;
-        sc[k] = s;
-        mx = fmaxf(mx, s);
+        if (k < n) {
+            if (sub == 0) sc[k] = s;
+            mx = fmaxf(mx, s);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -116,28 +130,30 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
     if (lane == 0) red[4 + warp] = sum;
     __syncthreads();
     sum = (red[4] + red[5]) + (red[6] + red[7]);
-    // weighted sum: thread -> (dimension, key residue); HD divides 128
-    constexpr int GROUPS = 128 / HD;
-    const int c = tid % HD, g = tid / HD;
-    float acc = 0.f;
-    for (int k = g; k < n; k += GROUPS) acc = fmaf(sc[k], to_f<E>(vbase[(long long)k * d + c]), acc);
-    if (GROUPS > 1) {
-        __shared__ float partial[128];
-        partial[tid] = acc;
-        __syncthreads();
-        if (g == 0) {
+    // weighted sum: the same thread-to-row mapping, PER output dimensions per thread, keys strided by KPP
+    float acc[PER];
 #pragma unroll
-            for (int j = 1; j < GROUPS; j++) acc += partial[j * HD + c];
-        }
+    for (int i = 0; i < PER; i++) acc[i] = 0.f;
+    for (int k = grp; k < n; k += KPP) {
+        const float p = sc[k];
+        const uint4 raw = *reinterpret_cast<const uint4*>(vbase + (long long)k * d + sub * PER);
+        const E* e = reinterpret_cast<const E*>(&raw);
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] = fmaf(p, to_f<E>(e[i]), acc[i]);
     }
-    if (g == 0) {
-        float o = acc / sum;
+#pragma unroll
+    for (int i = 0; i < PER; i++) part[(grp * TPR + sub) * PER + i] = acc[i];
+    __syncthreads();
+    if (tid < HD) {
+        float o = 0.f;
+#pragma unroll 4
+        for (int g = 0; g < KPP; g++) o += part[g * HD + tid];
+        o /= sum;
         if (round_out) o = round_tf32(o);
-        out[(long long)b * d + h * HD + c] = from_f<E>(o);
+        out[(long long)b * d + h * HD + tid] = from_f<E>(o);
     }
 }
 
-// tokens_out[b, *step] = next[b]; then advance the position and the step counter
 struct decode_sink {          // lives in device memory so that a captured step does not depend on call arguments
     int32_t* tokens_out;      // (B, n_cols) or null
     int n_cols;
@@ -203,7 +219,7 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
     const int d = dec->m.d, H = dec->m.heads, hd = d / H, B = dec->B;
     const size_t layer_elems = (size_t)B * dec->max_len * d;
     const float inv = 1.f / sqrtf((float)hd);
-    const size_t smem = (size_t)(hd + dec->max_len) * sizeof(float);
+    const size_t smem = (size_t)dec->max_len * sizeof(float);
     const int round_out = dec->m.prec == TLNN_PREC_TF32;
 #define DA_CASE(E, HDV)                                                                                              \
     TL_LAUNCH(ctx, "decode_attention", decode_attention_kernel<E, HDV><<<B * H, 128, smem, ctx->stream>>>(           \
