@@ -5,7 +5,7 @@
 //              maximum and the row sum need no shuffles), warps 4-7 the same for stream 1;
 //   warps 8-9  MMA issuers, one thread per stream: S_j = Q K_j^T (128 x 64 x 64) into one of the stream's two S
 //              buffers in TMEM, and O += P_j V_j (128 x 64 x 64) with P taken from shared memory and V read as an
-//              MN-major operand;
+//              MN-major operand; S_{j+2} is issued as soon as S_j has been read, P_j V_j when P_j is complete;
 //   warp 10    TMA producer: Q once, then K / V tiles of 64 keys through a six-stage ring.
 // S is double-buffered per stream, so S_{j+1} and S_{j+2} are computed while the softmax warps work on S_j; the
 // softmax of a tile waits only for its own S (and, rarely, for the accumulator to be quiescent), never for the P V
@@ -41,6 +41,12 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two float32 -> packed bf16 pair, round to nearest (ties up) with integer adds and one byte permute, which keeps the
+// conversions off the special-function unit.  Inputs are finite and non-negative.
+__device__ __forceinline__ uint32_t pack_bf16_rn(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
 // Instruction descriptors: D float32, A and B bf16, M = 128, N = 64.  S: both operands K-major.  PV: A K-major (P),
 // B MN-major (V rows are keys, the head dimension is contiguous).
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
@@ -59,7 +65,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     uint64_t* s_full = kv_empty + KV_STAGES;         // [2][2] S_j is in TMEM buffer j & 1
     uint64_t* p_full = s_full + 4;                   // [2][2] P_j is in shared-memory buffer j & 1 (and S_j has been read)
     uint64_t* pv_done = p_full + 4;                  // [2][2] O includes P_j V_j (and P buffer j & 1 may be rewritten)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 4);
+    uint64_t* s_free = pv_done + 4;                  // [2][2] S_j has been read into registers: its TMEM buffer may be rewritten
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,7 +87,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         tma_prefetch_desc(&tm_kv);
         mbar_init(q_full, 1);
         for (int i = 0; i < KV_STAGES; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 2); }
-        for (int i = 0; i < 4; i++) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
+        for (int i = 0; i < 4; i++) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); mbar_init(&s_free[i], 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -115,8 +122,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         }
     } else if (warp >= 8) {
         // ------------------------------------------------------------------ MMA issuers: one thread per stream
-        // Order per stream: S_0, S_1, then for every tile j: wait P_j -> O += P_j V_j -> give the key tile back ->
-        // S_{j+2}.  Both issuers wait on the same kv_full phases; a key tile returns to the producer after two
+        // Order per stream: S_0, S_1, then for every tile j: wait until S_j has been read -> S_{j+2}; wait P_j ->
+        // O += P_j V_j -> give the key tile back.  Both issuers wait on the same kv_full phases; a key tile returns to the producer after two
         // arrivals on kv_empty, one per stream (a stream that does not need a tile arrives for it once it is loaded).
         if (lane == 0) {
             const int s = warp - 8;
@@ -146,6 +153,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
             if (ok && nt > 0) ok = issue_s(0);
             if (ok && nt > 1) ok = issue_s(1);
             for (int j = 0; j < nt && ok; j++) {
+                // the score buffer of tile j is free as soon as the softmax warps hold S_j in registers: compute S_{j+2}
+                // into it right away, long before P_j is finished
+                if (j + 2 < nt) {
+                    if (!mbar_wait(&s_free[s * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag, err, 210)) { ok = false; break; }
+                    tc_fence_after();
+                    ok = issue_s(j + 2);
+                    if (!ok) break;
+                }
                 if (!mbar_wait(&p_full[s * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag, err, 204)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t p_desc = p_desc0 + (uint64_t)(j & 1) * P_UNITS;
@@ -156,7 +171,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 umma_commit(&pv_done[s * 2 + (j & 1)]);
                 umma_commit(&kv_empty[use_stage]);
                 if (++use_stage == KV_STAGES) use_stage = 0;
-                if (j + 2 < nt) ok = issue_s(j + 2);
             }
             // key tiles only the other stream needs: arrive for each once it is known to be loaded
             for (int t = nt; t < n_max && ok; t++) {
@@ -193,6 +207,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
             tmem_ld32_issue(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
             tmem_ld32_issue(s_tmem + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
             tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[s * 2 + bsel]);
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < BK; i++) {
@@ -238,6 +255,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
             }
             // probabilities against the reference, row sum, bf16 P into the K-major 128-byte-swizzled operand layout
             uint8_t* p_row = smem + OFF_P + (s * 2 + bsel) * P_BYTES + r * 128;
+            // (Packed ex2.approx.bf16x2 was measured slower than the float32 instruction here, and a P operand in f16
+            // against V in bf16 is rejected by tcgen05.mma as an illegal instruction: A and B share one 16-bit format.)
             float lp[8];
 #pragma unroll
             for (int g = 0; g < 8; g++) {
@@ -246,14 +265,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 for (int i = 0; i < 8; i++) pv[i] = ex2(fmaf(__uint_as_float(sc[g * 8 + i]), scale_log2, -m_ref));
                 lp[g] = ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
                 uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(pv[2], pv[3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(pv[4], pv[5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(pv[6], pv[7]);
-                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                pk.x = pack_bf16_rn(pv[0], pv[1]);
+                pk.y = pack_bf16_rn(pv[2], pv[3]);
+                pk.z = pack_bf16_rn(pv[4], pv[5]);
+                pk.w = pack_bf16_rn(pv[6], pv[7]);
                 // keys 8g .. 8g+7: 16-byte unit g of the row, XOR-swizzled by the row
                 *reinterpret_cast<uint4*>(p_row + ((g ^ (r & 7)) << 4)) = pk;
             }
