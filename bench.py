@@ -42,9 +42,11 @@ from torchless_nn_b200 import workloads as wl  # noqa: E402
 METRIC = "gpt_prefill_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant GEMM class from an ncu capture, scaled to
-# this workload's mean launch (see profiles/); None until a capture exists.
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMM launches of one block, from the ncu capture summarised
+# in profiles/gemm_tcgen05_c3_prefill.md (c3: 16384 rows, width 768): 411.7 MB.  Traffic grows with rows x width, so a
+# workload's mean launch is estimated as that figure scaled by (rows x width) / (16384 x 768), times layers, plus the
+# head's operand and arg-max candidate bytes, over the number of GEMM launches.
+GEMM_BLOCK_TRAFFIC_C3 = 411.7e6
 
 
 def measured_peak():
@@ -297,7 +299,12 @@ def run_b200(args, spec):
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all tile widths)", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_how,
-                "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "launches": gemm_launches,
+                "traffic": ((GEMM_BLOCK_TRAFFIC_C3 * (n_local * d) / (16384.0 * 768.0)) * L
+                            + n_local * d * 2.0 + spec.vocab * d * 2.0 + n_local * 394 * 8.0) / (4 * L + 1),
+                "traffic_note": "mean DRAM bytes per GEMM launch, scaled from the c3 ncu capture by rows x width",
+                "algorithmic_bytes_per_launch": (n_local * (d * 2.0 * 7 + d * 4.0 * 4 + 3 * d * 2.0 + 4 * d * 2.0) * L
+                                                 + 12.0 * d * d * 2 * L + n_local * d * 2.0 + spec.vocab * d * 2.0) / (4 * L + 1),
+                "launches": gemm_launches,
                 "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
                 "share_of_step": gemm_ms / float(ms.value) if ms.value else None,
                 "kernel_classes_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(classes.items())},
