@@ -46,6 +46,8 @@ extern "C" int tlnn_init(int device, tlnn_ctx** out) {
     TL_CUDA(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &keep));
     TL_CUDA(cudaMalloc(&c->d_err, sizeof(tlnn_dev_err)));
     TL_CUDA(cudaMemset(c->d_err, 0, sizeof(tlnn_dev_err)));
+    TL_CUDA(cudaMalloc(&c->d_sched, 256));
+    TL_CUDA(cudaMemset(c->d_sched, 0, 256));
     TL_CUDA(cudaMallocHost(&c->h_err, sizeof(tlnn_dev_err)));
     memset(c->h_err, 0, sizeof(tlnn_dev_err));
     TL_CUDA(cudaEventCreate(&c->prof_a));
@@ -62,6 +64,7 @@ extern "C" int tlnn_shutdown(tlnn_ctx* ctx) {
     for (auto& e : ctx->event_pool) cudaEventDestroy(e);
     if (ctx->ws) cudaFree(ctx->ws);
     cudaFree(ctx->d_err);
+    cudaFree(ctx->d_sched);
     cudaFreeHost(ctx->h_err);
     cudaEventDestroy(ctx->prof_a);
     cudaEventDestroy(ctx->prof_b);

@@ -41,6 +41,7 @@ struct tlnn_ctx {
     cudaMemPool_t pool = nullptr;
     tlnn_dev_err* d_err = nullptr;     // device memory
     tlnn_dev_err* h_err = nullptr;     // pinned host mirror
+    int* d_sched = nullptr;            // device work counter of the persistent attention kernel (zeroed per launch)
     long long launches = 0;
     // grow-only scratch arena used by the composite layer calls (stream-ordered reuse)
     char* ws = nullptr;

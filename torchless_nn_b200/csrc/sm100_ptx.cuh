@@ -54,7 +54,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  Returns false (after recording the failure and raising the CTA's abort flag) when the barrier
 // did not flip within WAIT_LIMIT_NS or another role of this CTA already gave up.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+// (Kept out of line unless TLNN_INLINE_WAITS is defined: a kernel that re-partitions registers with setmaxnreg cannot
+// make function calls.)
+#ifdef TLNN_INLINE_WAITS
+static __device__ __forceinline__ bool mbar_wait_slow(
+#else
+static __device__ __noinline__ bool mbar_wait_slow(
+#endif
+    uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                             tlnn_dev_err* err, int site) {
     unsigned long long t0 = globaltimer_ns();
     for (;;) {
