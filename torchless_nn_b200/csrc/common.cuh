@@ -154,7 +154,7 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
 // Tile width the GEMM will pick for this problem, and the number of arg-max candidates it leaves per row
 // (the partial buffer holds rows x tl_gemm_argmax_parts float2 entries).
 int tl_gemm_bn(int M, int N, int sm_count);
-int tl_gemm_argmax_parts(int M, int N, int sm_count);
+int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count);
 
 // Fused attention on a packed projection buffer: qkv is (B, T, 3d) with columns [0,d) Q, [d,2d) K, [2d,3d) V
 // and head h at columns h*hd..(h+1)*hd inside each third.  out is (B, T, d) of the same kind.

@@ -311,7 +311,7 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     dec->max_len = max_len;
     const int d = m->d, prec = m->prec;
     const size_t es = esize(prec);
-    dec->n_parts = tl_gemm_argmax_parts(B, m->vocab, ctx->sm_count);
+    dec->n_parts = tl_gemm_argmax_parts(prec, B, m->vocab, ctx->sm_count);
     // carve one allocation
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };

@@ -16,6 +16,8 @@
 // context's error word, raises a CTA-wide abort flag, and all roles fall through to the common exit, where the
 // TMEM allocation is returned.
 #include "sm100_ptx.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -26,6 +28,9 @@ constexpr int ROW_BYTES = 128;      // one swizzle-128B row of K: 64 bf16 or 32 
 constexpr int MMA_K_BYTES = 32;     // K extent of one tcgen05.mma: 16 bf16 or 8 tf32
 constexpr int GROUP_M = 8;          // rasterisation: tiles are walked in groups of GROUP_M row-blocks
 constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, eight epilogue warps
+#ifndef PAIR_TMEM_COLS
+#define PAIR_TMEM_COLS 512
+#endif
 
 template <int BN> struct Cfg {
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
@@ -137,11 +142,21 @@ enum {
 //                           instruction writes four whole row segments.
 // The bias and the residual of a chunk are requested before its accumulator is waited for, and the accumulator
 // buffer goes back to the MMA warp as soon as this warp's last chunk is in registers.
-template <int BN, int MODE>
+// PAIR: the CTA is one half of a cta_group::2 pair.  Tiles are walked per cluster over (row pairs, n_tiles); this CTA
+// owns row block 2 * pair + rank, and the accumulator buffer is given back on the leader CTA's barrier.
+template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M, int N, int m_tiles, int n_tiles,
                                               int total_tiles, int warp, int lane, uint32_t tmem_base, float* staging,
                                               uint64_t* acc_full, uint64_t* acc_empty, volatile int* abort_flag,
                                               tlnn_dev_err* err) {
+    const int tile0 = PAIR ? (int)cluster_id_x() : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
+    const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
+    uint32_t acc_empty_leader[2] = {0u, 0u};
+    if (PAIR) {
+        acc_empty_leader[0] = map_to_cta(smem_u32(&acc_empty[0]), 0);
+        acc_empty_leader[1] = map_to_cta(smem_u32(&acc_empty[1]), 0);
+    }
     constexpr int NCHUNK = BN / 32;
     constexpr bool GENERIC = MODE == EPI_GENERIC;
     constexpr bool HAS_OUT = MODE != EPI_ARGMAX;
@@ -166,8 +181,9 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     }
 
     int local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
-        const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+    for (int t = tile0; t < total_tiles; t += tile_step, local++) {
+        TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+        if (PAIR) tc.m_blk = tc.m_blk * 2 + cta_rank;
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
         const int n0 = tc.n_blk * BN;
@@ -214,7 +230,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                 // every accumulator column this warp needs is in registers: hand the buffer back
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(acc_empty_leader[buf]);
+                    else mbar_arrive(&acc_empty[buf]);
+                }
             }
             float v[32];
 #pragma unroll
@@ -297,7 +316,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
             // no live chunk in this tile: the MMA warp still needs this warp's arrival for the buffer
             if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 105)) return;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(acc_empty_leader[buf]);
+                else mbar_arrive(&acc_empty[buf]);
+            }
         }
         if (want_argmax) {
             const long long my_row = row_base + lane;
@@ -422,6 +444,155 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
+// ---- the pair kernel (bf16, 256 x 256 tiles over two SMs) ---------------------------------------------------------------
+// A cluster of two CTAs computes a 256 x 256 tile: each CTA loads its own 128 rows of A and one half (128 rows) of
+// the W tile, the leader CTA (rank 0) issues tcgen05.mma.cta_group::2, which reads both halves of W from both CTAs'
+// shared memory, and each CTA ends up with its 128 x 256 accumulator in its own TMEM.  Per k-block a CTA writes and
+// reads 32 KB of shared memory instead of 48 KB, which lifts the shared-memory bandwidth limit of the one-CTA tile.
+// Barriers: `full` lives in the leader and counts the bytes of all four loads; `empty` and `acc_full` exist in both
+// CTAs and the leader's MMA thread commits to each; `acc_empty` lives in the leader and collects the sixteen
+// epilogue warps of the pair.  Both CTAs pass one cluster barrier after set-up and one before they return their
+// TMEM; every role reaches the second one on every path, time-outs included.
+struct PairCfg {
+    static constexpr int BN = 256;
+    static constexpr int STAGES = 6;
+    static constexpr uint32_t A_BYTES = BM * ROW_BYTES;            // 16 KB: this CTA's rows of A
+    static constexpr uint32_t B_BYTES = (BN / 2) * ROW_BYTES;      // 16 KB: this CTA's half of the W tile
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t TMEM_COLS = PAIR_TMEM_COLS;
+    static constexpr uint32_t BAR_BYTES = 256;
+    static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const tl_gemm_epilogue ep, int M, int N, int K, int m_pairs, int n_tiles, tlnn_dev_err* err) {
+    using C = PairCfg;
+    constexpr int STAGES = C::STAGES;
+    constexpr int BN = C::BN;
+    constexpr int K_ELEMS = 64;
+    constexpr int ACC_BUFS = C::TMEM_COLS / BN;            // 2 (1 while the allocation semantics are being verified)
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int total_tiles = m_pairs * n_tiles;
+    const int num_k = (K + K_ELEMS - 1) / K_ELEMS;
+    const int tile0 = (int)cluster_id_x(), tile_step = (int)cluster_count_x();
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 16);     // one arrival per epilogue warp of the pair
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       // the peer's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one per CTA)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+                const TileCoord tc = tile_coord(t, m_pairs, n_tiles);
+                const int row_a = (tc.m_blk * 2 + (int)rank) * BM;
+                const int row_b = tc.n_blk * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, err, 111)) { ok = false; break; }
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * C::STAGE_BYTES);
+                    const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * C::STAGE_BYTES);
+                    tma_load_2d_pair(sa, &tmA, bar, kb * K_ELEMS, row_a);
+                    tma_load_2d_pair(sa + C::A_BYTES, &tmB, bar, kb * K_ELEMS, row_b);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            // D float32, A / B bf16 K-major, N = 256, M = 256 over the pair
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = tile0; t < total_tiles && ok; t += tile_step, local++) {
+                const int buf = local % ACC_BUFS;
+                const uint32_t buf_phase = (uint32_t)(local / ACC_BUFS) & 1u;
+                if (!mbar_wait(&acc_empty[buf], buf_phase ^ 1u, abort_flag, err, 112)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag, err, 113)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * C::STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc(sa);
+                    const uint64_t b_desc = make_smem_desc(sa + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < ROW_BYTES / MMA_K_BYTES; k++)
+                        umma_pair_f16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                    // the stage is free in both CTAs once these MMAs have read it
+                    const uint32_t eb = smem_u32(&empty_bar[stage]);
+                    umma_commit_pair(map_to_cta(eb, 0));
+                    umma_commit_pair(map_to_cta(eb, 1));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    const uint32_t fb = smem_u32(&acc_full[buf]);
+                    umma_commit_pair(map_to_cta(fb, 0));
+                    umma_commit_pair(map_to_cta(fb, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (8 warps per CTA, 128 rows x 256 columns)
+        if (ACC_BUFS == 2) {
+            epilogue_warp<BN, MODE, true>(ep, M, N, m_pairs, n_tiles, total_tiles, warp, lane, tmem_base,
+                                          reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       // nobody returns TMEM or leaves while the peer may still touch this CTA
+    if (warp == 1) {
+        tc_fence_after();
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------------
 int pick_bn(int M, int N, int sm_count) {
     const int m_tiles = (M + BM - 1) / BM;
@@ -444,6 +615,64 @@ int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl
     TL_LAUNCH(ctx, name, kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM, ctx->stream>>>(ta, tb, ep, M, N, K, m_tiles, n_tiles,
                                                                                    ctx->d_err));
     return TLNN_OK;
+}
+
+// Persistent clusters of the pair kernel that fit on the device at once (queried once per epilogue variant).
+template <int MODE>
+int launch_pair(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep, int M, int N, int K) {
+    auto kernel = gemm_tcgen05_pair_kernel<MODE>;
+    const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PairCfg::BN - 1) / PairCfg::BN;
+    const long long total = (long long)m_pairs * n_tiles;
+    TL_REQUIRE(total < (1ll << 31), "gemm: too many tiles");
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = PairCfg::SMEM;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM));
+        cfg.gridDim = dim3(2 * (ctx->sm_count / 2));
+        int n = 0;
+        TL_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        TL_REQUIRE(n > 0, "gemm: no cluster of two CTAs fits on this device");
+        max_clusters = n < ctx->sm_count / 2 ? n : ctx->sm_count / 2;
+    }
+    const int clusters = (int)(total < max_clusters ? total : max_clusters);
+    cfg.gridDim = dim3(2 * clusters);
+    TL_LAUNCH(ctx, "gemm_bf16_pair", TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ep, M, N, K, m_pairs, n_tiles, ctx->d_err)));
+    return TLNN_OK;
+}
+
+int launch_pair_mode(tlnn_ctx* ctx, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep,
+                     int M, int N, int K) {
+    switch (mode) {
+        case EPI_BF16: return launch_pair<EPI_BF16>(ctx, ta, tb, ep, M, N, K);
+        case EPI_BF16_GELU: return launch_pair<EPI_BF16_GELU>(ctx, ta, tb, ep, M, N, K);
+        case EPI_F32_RES: return launch_pair<EPI_F32_RES>(ctx, ta, tb, ep, M, N, K);
+        case EPI_ARGMAX: return launch_pair<EPI_ARGMAX>(ctx, ta, tb, ep, M, N, K);
+        default: return launch_pair<EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);
+    }
+}
+
+// The pair kernel pays off when there are enough 256 x 256 tiles to keep every cluster busy for several rounds.
+// TLNN_GEMM_PAIR=0 switches it off, =force uses it for every bf16 product.
+bool use_pair(int sm_count, int prec, int M, int N) {
+    static int policy = -1;
+    if (policy < 0) {
+        const char* e = getenv("TLNN_GEMM_PAIR");
+        policy = e == nullptr ? 1 : (strcmp(e, "0") == 0 ? 0 : (strcmp(e, "force") == 0 ? 2 : 1));
+    }
+    if (prec != TLNN_PREC_BF16 || policy == 0) return false;
+    if (policy == 2) return true;
+    const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + PairCfg::BN - 1) / PairCfg::BN);
+    return pick_bn(M, N, sm_count) == 256 && tiles >= 2ll * sm_count;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -481,8 +710,8 @@ int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const C
 }  // namespace
 
 int tl_gemm_bn(int M, int N, int sm_count) { return pick_bn(M, N, sm_count); }
-int tl_gemm_argmax_parts(int M, int N, int sm_count) {
-    const int bn = pick_bn(M, N, sm_count);
+int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count) {
+    const int bn = use_pair(sm_count, prec, M, N) ? PairCfg::BN : pick_bn(M, N, sm_count);
     return 2 * ((N + bn - 1) / bn);     // two epilogue warps cover each row of a tile
 }
 
@@ -494,6 +723,12 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
     TL_REQUIRE((K * esz) % 16 == 0, "gemm: the contraction length %d must be a multiple of %d elements", K, 16 / esz);
     TL_REQUIRE((lda * esz) % 16 == 0 && (ldw * esz) % 16 == 0, "gemm: operand pitches must be multiples of 16 bytes");
     TL_REQUIRE(((uintptr_t)a & 15u) == 0 && ((uintptr_t)w & 15u) == 0, "gemm: operands must be 16-byte aligned");
+    if (use_pair(ctx->sm_count, prec, M, N)) {
+        CUtensorMap ta, tb;
+        TL_TRY(make_tile_map(&ta, true, a, M, K, lda, BM));
+        TL_TRY(make_tile_map(&tb, true, w, N, K, ldw, PairCfg::BN / 2));
+        return launch_pair_mode(ctx, pick_mode(ep, N), ta, tb, ep, M, N, K);
+    }
     const int bn = pick_bn(M, N, ctx->sm_count);
     CUtensorMap ta, tb;
     TL_TRY(make_tile_map(&ta, prec == TLNN_PREC_BF16, a, M, K, lda, BM));

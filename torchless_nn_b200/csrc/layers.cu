@@ -97,7 +97,7 @@ int check_block_shape(int B, int T, int d, int heads) {
 size_t head_ws_bytes(tlnn_ctx* ctx, int prec, long long rows, int d, int vocab, bool want_tokens) {
     size_t n = tl_ws_round((size_t)rows * d * op_size(prec));
     if (want_tokens) {
-        n += tl_ws_round((size_t)rows * tl_gemm_argmax_parts((int)rows, vocab, ctx->sm_count) * sizeof(float2));
+        n += tl_ws_round((size_t)rows * tl_gemm_argmax_parts(prec, (int)rows, vocab, ctx->sm_count) * sizeof(float2));
     }
     return n;
 }
@@ -109,7 +109,7 @@ int run_head(tlnn_ctx* ctx, int prec, const void* a, const void* table_t, const 
     e.bias = bias; e.out = logits; e.ldo = vocab; e.out_kind = TL_OUT_F32;
     int n_parts = 0;
     if (tokens) {
-        n_parts = tl_gemm_argmax_parts((int)rows, vocab, ctx->sm_count);
+        n_parts = tl_gemm_argmax_parts(prec, (int)rows, vocab, ctx->sm_count);
         e.argmax_partials = cur.take<float2>((size_t)rows * n_parts);
     }
     TL_TRY(tl_gemm(ctx, prec, a, d, table_t, d, (int)rows, vocab, d, e));

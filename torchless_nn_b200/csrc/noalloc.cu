@@ -31,7 +31,7 @@ extern "C" int tlnn_logits_tokens_noalloc(tlnn_ctx* ctx, int prec, const float* 
     TL_NOTNULL(x);
     TL_CUDA(cudaSetDevice(ctx->device));
     const size_t esz = prec == TLNN_PREC_BF16 ? 2 : 4;
-    const int n_parts = tl_gemm_argmax_parts((int)rows, vocab, ctx->sm_count);
+    const int n_parts = tl_gemm_argmax_parts(prec, (int)rows, vocab, ctx->sm_count);
     const size_t operand_bytes = tl_ws_round((size_t)rows * d * esz);
     const size_t partial_bytes = (size_t)rows * n_parts * sizeof(float2);
     if (operand_bytes + partial_bytes > (size_t)TLNN_NOALLOC_SCRATCH_BYTES) {
