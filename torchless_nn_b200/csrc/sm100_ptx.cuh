@@ -145,8 +145,8 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// TMA load whose completion bytes are counted on an mbarrier of either CTA of the pair (no multicast: the tile
-// lands in this CTA's shared memory only).
+// TMA load whose completion bytes are counted on an mbarrier of either CTA of the pair; the tile lands in this
+// CTA's shared memory only.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
