@@ -297,7 +297,7 @@ def run_b200(args, spec):
     gemm_flops = args.steps * n_local * (L * 24.0 * d * d + 2.0 * d * spec.vocab)
     peak, peak_how = measured_peak()
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all tile widths)", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel / gemm_tcgen05_kernel (all GEMM launches)", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_how,
                 "traffic": ((GEMM_BLOCK_TRAFFIC_C3 * (n_local * d) / (16384.0 * 768.0)) * L
                             + n_local * d * 2.0 + spec.vocab * d * 2.0 + n_local * 394 * 8.0) / (4 * L + 1),
