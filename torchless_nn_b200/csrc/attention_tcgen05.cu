@@ -78,6 +78,17 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
 }
 
+// Store 16 registers per thread to 32 lanes x 16 columns of TMEM.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 // Instruction descriptors: D float32, A and B bf16, M = 128, N = 64.  S: both operands K-major.  PV: A K-major (P),
 // B MN-major (V rows are keys, the head dimension is contiguous).
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
@@ -283,6 +294,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 __syncwarp();
                 tc_fence_after();
                 const int k0 = j * BK;
+                if (CAUSAL && k0 > warp_row_lo + 31) {
+                    // every key of this tile lies beyond every row of this warp (upper half of the block's last tile):
+                    // the probabilities are zero, nothing else changes
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar.s_free);
+                    if (j > 0) {
+                        if (!mbar_wait(&bar.pv_done, par ^ 1u, abort_flag, err, 207)) { ok = false; break; }
+                        __syncwarp();
+                        tc_fence_after();
+                    }
+                    uint32_t zero[BK / 4];
+#pragma unroll
+                    for (int i = 0; i < BK / 4; i++) zero[i] = 0u;
+                    tmem_st16(p_tmem, zero);
+                    tmem_st16(p_tmem + (uint32_t)(BK / 4), zero);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar.p_full);
+                    continue;
+                }
                 uint32_t sc[BK];
                 tmem_ld32_issue(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
                 tmem_ld32_issue(s_tmem + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
@@ -339,18 +372,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 asm("mov.b64 %0, {%1, %1};" : "=l"(negm2) : "f"(-m_ref));
 #pragma unroll
                 for (int i = 0; i < 4; i++) ls[i] = 0ull;
-                uint32_t pk[BK / 2];
+                // The P columns were last read by P_{j-1} V_{j-1} (for j = 0 the previous item's epilogue waited).  P goes
+                // to TMEM in two halves of 32 keys, so that the packed registers of the first half are free again
+                // while the second half is computed.
+                auto exp_half = [&](int h, uint32_t (&pk)[BK / 4]) {
 #pragma unroll
-                for (int i = 0; i < BK / 2; i++) {
-                    uint64_t in, xs, pp;
-                    float x0, x1;
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(in) : "r"(sc[2 * i]), "r"(sc[2 * i + 1]));
-                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(xs) : "l"(in), "l"(scale2), "l"(negm2));
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(xs));
-                    const float p0 = ex2(x0), p1 = ex2(x1);
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(pp) : "f"(p0), "f"(p1));
-                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(ls[i & 3]) : "l"(ls[i & 3]), "l"(pp));
-                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[i]) : "f"(p1), "f"(p0));      // key 2i in the low half
+                    for (int q = 0; q < BK / 4; q++) {
+                        const int i = h * (BK / 4) + q;
+                        uint64_t in, xs, pp;
+                        float x0, x1;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(in) : "r"(sc[2 * i]), "r"(sc[2 * i + 1]));
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(xs) : "l"(in), "l"(scale2), "l"(negm2));
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(xs));
+                        const float p0 = ex2(x0), p1 = ex2(x1);
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(pp) : "f"(p0), "f"(p1));
+                        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(ls[i & 3]) : "l"(ls[i & 3]), "l"(pp));
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[q]) : "f"(p1), "f"(p0));      // key 2i in the low half
+                    }
+                };
+                {
+                    uint32_t pk[BK / 4];
+                    exp_half(0, pk);
+                    if (j > 0) {
+                        if (!mbar_wait(&bar.pv_done, par ^ 1u, abort_flag, err, 207)) { ok = false; break; }
+                        __syncwarp();
+                        tc_fence_after();
+                    }
+                    tmem_st16(p_tmem, pk);
+                }
+                {
+                    uint32_t pk[BK / 4];
+                    exp_half(1, pk);
+                    tmem_st16(p_tmem + (uint32_t)(BK / 4), pk);
                 }
                 {
                     float a0, a1, a2, a3, a4, a5, a6, a7;
@@ -360,13 +413,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                     asm("mov.b64 {%0, %1}, %2;" : "=f"(a6), "=f"(a7) : "l"(ls[3]));
                     l_run += ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
                 }
-                // the P columns were last read by P_{j-1} V_{j-1} (for j = 0 the previous item's epilogue waited)
-                if (j > 0) {
-                    if (!mbar_wait(&bar.pv_done, par ^ 1u, abort_flag, err, 207)) { ok = false; break; }
-                    __syncwarp();
-                    tc_fence_after();
-                }
-                tmem_st32(p_tmem, pk);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
