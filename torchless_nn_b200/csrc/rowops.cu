@@ -121,6 +121,7 @@ __global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* 
     }
     float var = warp_sum(q) / (float)d;
     float stdv = sqrtf(var + eps);
+    const float inv = 1.f / stdv;
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
     const float4* b4 = reinterpret_cast<const float4*>(beta);
 #pragma unroll
@@ -129,10 +130,19 @@ __global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* 
         if (c < nvec) {
             float4 g = __ldg(g4 + c), b = __ldg(b4 + c);
             float4 r;
-            r.x = g.x * (v[i].x / stdv) + b.x;
-            r.y = g.y * (v[i].y / stdv) + b.y;
-            r.z = g.z * (v[i].z / stdv) + b.z;
-            r.w = g.w * (v[i].w / stdv) + b.w;
+            if (KIND == TL_OUT_BF16) {
+                // the result is rounded to 8 significant bits: one division per row and a multiplication per
+                // element instead of a division per element (which made the kernel issue-bound)
+                r.x = g.x * (v[i].x * inv) + b.x;
+                r.y = g.y * (v[i].y * inv) + b.y;
+                r.z = g.z * (v[i].z * inv) + b.z;
+                r.w = g.w * (v[i].w * inv) + b.w;
+            } else {
+                r.x = g.x * (v[i].x / stdv) + b.x;
+                r.y = g.y * (v[i].y / stdv) + b.y;
+                r.z = g.z * (v[i].z / stdv) + b.z;
+                r.w = g.w * (v[i].w / stdv) + b.w;
+            }
             store4<KIND>(out, row * d + c * 4, r);
         }
     }
