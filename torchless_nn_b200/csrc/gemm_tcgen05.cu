@@ -38,7 +38,7 @@ template <int BN> struct Cfg {
     static constexpr uint32_t B_BYTES = BN * ROW_BYTES;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr uint32_t BAR_BYTES = 256;
+    static constexpr uint32_t BAR_BYTES = 1024;      // keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
     static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;     // eight 4 KB staging tiles
     static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024 /*alignment slack*/;
 };
@@ -131,8 +131,13 @@ enum {
     EPI_BF16 = 1,        // bf16 out (+bias)                         N % 32 == 0, 16-byte aligned rows
     EPI_BF16_GELU = 2,   // bf16 out, bias, tanh-GeLU (hardware tanh)  same conditions
     EPI_F32_RES = 3,     // float32 out (+bias) + float32 residual     same conditions, residual rows aligned too
-    EPI_ARGMAX = 4       // no output, (+bias), per-row arg-max candidates; ragged N allowed
+    EPI_ARGMAX = 4,      // no output, (+bias), per-row arg-max candidates; ragged N allowed
+    EPI_F32_ACCUM = 5    // out += acc (+bias): the residual IS the output buffer (in-place residual stream)
 };
+// EPI_BF16, EPI_BF16_GELU and EPI_F32_ACCUM leave the tile through TMA: the warp writes its 32-row slab into its
+// staging tile in the 128-byte-swizzled layout and one lane issues a bulk tensor store (bf16: 64 columns at a time) or a
+// bulk tensor reduce-add (float32: the memory system adds the tile to the residual in place, so the residual never
+// travels to the SM).  No per-thread global loads or stores, no second pass over the staging tile.
 
 // Two warps share each 32-row quarter of the tile (a warp may only read the TMEM lanes of its warp-id mod 4) and take
 // the even / odd 32-column chunks.  Per chunk:
@@ -148,7 +153,7 @@ template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M, int N, int m_tiles, int n_tiles,
                                               int total_tiles, int warp, int lane, uint32_t tmem_base, float* staging,
                                               uint64_t* acc_full, uint64_t* acc_empty, volatile int* abort_flag,
-                                              tlnn_dev_err* err) {
+                                              tlnn_dev_err* err, const CUtensorMap* tm_out) {
     const int tile0 = PAIR ? (int)cluster_id_x() : (int)blockIdx.x;
     const int tile_step = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
     const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
@@ -160,6 +165,8 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     constexpr int NCHUNK = BN / 32;
     constexpr bool GENERIC = MODE == EPI_GENERIC;
     constexpr bool HAS_OUT = MODE != EPI_ARGMAX;
+    constexpr bool TMA_BF16 = MODE == EPI_BF16 || MODE == EPI_BF16_GELU;
+    constexpr bool TMA_OUT = TMA_BF16 || MODE == EPI_F32_ACCUM;
     const int ew = warp - 2;                        // 0..7
     const int quarter = warp & 3;
     const int half = ew >> 2;                       // 0: even chunks, 1: odd chunks
@@ -189,16 +196,18 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
         const int n0 = tc.n_blk * BN;
         const long long row_base = (long long)tc.m_blk * BM + quarter * 32;
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-        // live chunks of this warp: half, half + 2, ... while the chunk starts inside N
+        // live chunks of this warp: half, half + 2, ... while the chunk starts inside N; with bf16 TMA stores a warp
+        // takes pairs of adjacent chunks (64 columns = one 128-byte staging row): 2 half, 2 half + 1, 2 half + 4, ...
+        auto chunk_of = [&](int i) { return TMA_BF16 ? 2 * half + (i & 1) + 4 * (i >> 1) : half + 2 * i; };
         int n_live = 0;
-        for (int c = half; c < NCHUNK && n0 + c * 32 < N; c += 2) n_live++;
+        while (chunk_of(n_live) < NCHUNK && n0 + chunk_of(n_live) * 32 < N) n_live++;
 
         float best = -INFINITY;
         int best_i = 0x7fffffff;
         bool waited = false;
 #pragma unroll 1
         for (int i = 0; i < n_live; i++) {
-            const int chunk = half + 2 * i;
+            const int chunk = chunk_of(i);
             const int col0 = n0 + chunk * 32;
             const int ncols = min(32, N - col0);
             const bool full = ncols == 32;
@@ -218,7 +227,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                 }
             }
             if (!waited) {
-                if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 104)) return;
+                if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 104)) {
+                    if (TMA_OUT && lane == 0) tma_store_wait_all();
+                    return;
+                }
                 __syncwarp();
                 tc_fence_after();
                 waited = true;
@@ -254,7 +266,43 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                 for (int j = 0; j < 32; j++)
                     if (j < ncols && v[j] > best) { best = v[j]; best_i = col0 + j; }
             }
-            if (has_out) {
+            if (TMA_OUT) {
+                // the previous store may still be reading the staging tile
+                const bool first_of_tile = TMA_BF16 ? (i & 1) == 0 : true;
+                if (first_of_tile) {
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+                }
+                if (TMA_BF16) {
+                    // 32 columns = 64 bytes = units 4 (i & 1) .. + 3 of this thread's 128-byte staging row
+                    uint8_t* row = reinterpret_cast<uint8_t*>(stage_tile) + lane * 128;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        uint4 pk;
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk.x) : "f"(v[8 * u + 1]), "f"(v[8 * u + 0]));
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk.y) : "f"(v[8 * u + 3]), "f"(v[8 * u + 2]));
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk.z) : "f"(v[8 * u + 5]), "f"(v[8 * u + 4]));
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk.w) : "f"(v[8 * u + 7]), "f"(v[8 * u + 6]));
+                        *reinterpret_cast<uint4*>(row + ((((i & 1) * 4 + u) ^ (lane & 7)) << 4)) = pk;
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+                        *reinterpret_cast<float4*>(stage_tile + lane * 32 + ((u ^ (lane & 7)) << 2)) =
+                            make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+                }
+                const bool last_of_store = TMA_BF16 ? ((i & 1) == 1 || i == n_live - 1) : true;
+                if (last_of_store) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int x0 = TMA_BF16 ? n0 + (chunk & ~1) * 32 : col0;
+                        if (TMA_BF16) tma_store_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
+                        else tma_reduce_add_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
+                        tma_store_commit();
+                    }
+                }
+            } else if (has_out) {
 #pragma unroll
                 for (int u = 0; u < 8; u++)
                     *reinterpret_cast<float4*>(stage_tile + lane * 32 + ((u ^ (lane & 7)) << 2)) =
@@ -314,7 +362,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
         }
         if (n_live == 0) {
             // no live chunk in this tile: the MMA warp still needs this warp's arrival for the buffer
-            if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 105)) return;
+            if (!mbar_wait(&acc_full[buf], buf_phase, abort_flag, err, 105)) {
+                if (TMA_OUT && lane == 0) tma_store_wait_all();
+                return;
+            }
             __syncwarp();
             if (lane == 0) {
                 if (PAIR) mbar_arrive_cluster(acc_empty_leader[buf]);
@@ -328,13 +379,15 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                 ep.argmax_partials[(my_row * n_tiles + tc.n_blk) * 2 + half] = make_float2(best, __int_as_float(best_i));
         }
     }
+    if (TMA_OUT && lane == 0) tma_store_wait_all();
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------------------------
 template <int BN, bool TF32, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const tl_gemm_epilogue ep, int M, int N, int K, int m_tiles, int n_tiles, tlnn_dev_err* err) {
+                    const __grid_constant__ CUtensorMap tmOut, const tl_gemm_epilogue ep, int M, int N, int K, int m_tiles,
+                    int n_tiles, tlnn_dev_err* err) {
     using C = Cfg<BN>;
     constexpr int STAGES = C::STAGES;
     constexpr int K_ELEMS = TF32 ? 32 : 64;       // elements per 128-byte row
@@ -356,6 +409,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM) tma_prefetch_desc(&tmOut);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
@@ -432,7 +486,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else {
         // ------------------------------------------------------------------ epilogue (8 warps, 128 rows x BN columns)
         epilogue_warp<BN, MODE>(ep, M, N, m_tiles, n_tiles, total_tiles, warp, lane, tmem_base,
-                                reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err);
+                                reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err, &tmOut);
     }
 
     tc_fence_before();
@@ -460,7 +514,7 @@ struct PairCfg {
     static constexpr uint32_t B_BYTES = (BN / 2) * ROW_BYTES;      // 16 KB: this CTA's half of the W tile
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = PAIR_TMEM_COLS;
-    static constexpr uint32_t BAR_BYTES = 256;
+    static constexpr uint32_t BAR_BYTES = 1024;      // keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
     static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
     static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024;
 };
@@ -468,7 +522,8 @@ struct PairCfg {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const tl_gemm_epilogue ep, int M, int N, int K, int m_pairs, int n_tiles, tlnn_dev_err* err) {
+                         const __grid_constant__ CUtensorMap tmOut, const tl_gemm_epilogue ep, int M, int N, int K,
+                         int m_pairs, int n_tiles, tlnn_dev_err* err) {
     using C = PairCfg;
     constexpr int STAGES = C::STAGES;
     constexpr int BN = C::BN;
@@ -494,6 +549,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM) tma_prefetch_desc(&tmOut);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
@@ -579,7 +635,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // ------------------------------------------------------------------ epilogue (8 warps per CTA, 128 rows x 256 columns)
         if (ACC_BUFS == 2) {
             epilogue_warp<BN, MODE, true>(ep, M, N, m_pairs, n_tiles, total_tiles, warp, lane, tmem_base,
-                                          reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err);
+                                          reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err,
+                                          &tmOut);
         }
     }
 
@@ -611,7 +668,8 @@ int pick_bn(int M, int N, int sm_count) {
 }
 
 template <int BN, bool TF32, int MODE>
-int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep, int M, int N, int K) {
+int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const tl_gemm_epilogue& ep,
+           int M, int N, int K) {
     auto kernel = gemm_tcgen05_kernel<BN, TF32, MODE>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM));
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -620,14 +678,15 @@ int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     const char* name = TF32 ? (BN == 256 ? "gemm_tf32_n256" : BN == 128 ? "gemm_tf32_n128" : "gemm_tf32_n64")
                             : (BN == 256 ? "gemm_bf16_n256" : BN == 128 ? "gemm_bf16_n128" : "gemm_bf16_n64");
-    TL_LAUNCH(ctx, name, kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM, ctx->stream>>>(ta, tb, ep, M, N, K, m_tiles, n_tiles,
+    TL_LAUNCH(ctx, name, kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM, ctx->stream>>>(ta, tb, to, ep, M, N, K, m_tiles, n_tiles,
                                                                                    ctx->d_err));
     return TLNN_OK;
 }
 
 // Persistent clusters of the pair kernel that fit on the device at once (queried once per epilogue variant).
 template <int MODE>
-int launch_pair(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep, int M, int N, int K) {
+int launch_pair(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const tl_gemm_epilogue& ep,
+                int M, int N, int K) {
     auto kernel = gemm_tcgen05_pair_kernel<MODE>;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PairCfg::BN - 1) / PairCfg::BN;
     const long long total = (long long)m_pairs * n_tiles;
@@ -654,18 +713,19 @@ int launch_pair(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
     }
     const int clusters = (int)(total < max_clusters ? total : max_clusters);
     cfg.gridDim = dim3(2 * clusters);
-    TL_LAUNCH(ctx, "gemm_bf16_pair", TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ep, M, N, K, m_pairs, n_tiles, ctx->d_err)));
+    TL_LAUNCH(ctx, "gemm_bf16_pair", TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, to, ep, M, N, K, m_pairs, n_tiles, ctx->d_err)));
     return TLNN_OK;
 }
 
-int launch_pair_mode(tlnn_ctx* ctx, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep,
-                     int M, int N, int K) {
+int launch_pair_mode(tlnn_ctx* ctx, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+                     const tl_gemm_epilogue& ep, int M, int N, int K) {
     switch (mode) {
-        case EPI_BF16: return launch_pair<EPI_BF16>(ctx, ta, tb, ep, M, N, K);
-        case EPI_BF16_GELU: return launch_pair<EPI_BF16_GELU>(ctx, ta, tb, ep, M, N, K);
-        case EPI_F32_RES: return launch_pair<EPI_F32_RES>(ctx, ta, tb, ep, M, N, K);
-        case EPI_ARGMAX: return launch_pair<EPI_ARGMAX>(ctx, ta, tb, ep, M, N, K);
-        default: return launch_pair<EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);
+        case EPI_BF16: return launch_pair<EPI_BF16>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_BF16_GELU: return launch_pair<EPI_BF16_GELU>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_F32_RES: return launch_pair<EPI_F32_RES>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_F32_ACCUM: return launch_pair<EPI_F32_ACCUM>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_ARGMAX: return launch_pair<EPI_ARGMAX>(ctx, ta, tb, to, ep, M, N, K);
+        default: return launch_pair<EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);
     }
 }
 
@@ -699,20 +759,21 @@ int pick_mode(const tl_gemm_epilogue& ep, int N) {
     }
     if (ep.out_kind == TL_OUT_F32 && ep.residual != nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0 &&
         aligned16(ep.residual) && ep.ldr % 4 == 0)
-        return EPI_F32_RES;
+        return (ep.residual == ep.out && ep.ldr == ep.ldo) ? EPI_F32_ACCUM : EPI_F32_RES;
     return EPI_GENERIC;
 }
 
 template <int BN>
-int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const tl_gemm_epilogue& ep,
-              int M, int N, int K) {
-    if (tf32) return launch<BN, true, EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);      // FP32/TF32 shapes are small
+int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+              const tl_gemm_epilogue& ep, int M, int N, int K) {
+    if (tf32) return launch<BN, true, EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);      // FP32/TF32 shapes are small
     switch (mode) {
-        case EPI_BF16: return launch<BN, false, EPI_BF16>(ctx, ta, tb, ep, M, N, K);
-        case EPI_BF16_GELU: return launch<BN, false, EPI_BF16_GELU>(ctx, ta, tb, ep, M, N, K);
-        case EPI_F32_RES: return launch<BN, false, EPI_F32_RES>(ctx, ta, tb, ep, M, N, K);
-        case EPI_ARGMAX: return launch<BN, false, EPI_ARGMAX>(ctx, ta, tb, ep, M, N, K);
-        default: return launch<BN, false, EPI_GENERIC>(ctx, ta, tb, ep, M, N, K);
+        case EPI_BF16: return launch<BN, false, EPI_BF16>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_BF16_GELU: return launch<BN, false, EPI_BF16_GELU>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_F32_RES: return launch<BN, false, EPI_F32_RES>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_F32_ACCUM: return launch<BN, false, EPI_F32_ACCUM>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_ARGMAX: return launch<BN, false, EPI_ARGMAX>(ctx, ta, tb, to, ep, M, N, K);
+        default: return launch<BN, false, EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);
     }
 }
 
@@ -732,21 +793,24 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
     TL_REQUIRE((K * esz) % 16 == 0, "gemm: the contraction length %d must be a multiple of %d elements", K, 16 / esz);
     TL_REQUIRE((lda * esz) % 16 == 0 && (ldw * esz) % 16 == 0, "gemm: operand pitches must be multiples of 16 bytes");
     TL_REQUIRE(((uintptr_t)a & 15u) == 0 && ((uintptr_t)w & 15u) == 0, "gemm: operands must be 16-byte aligned");
+    const bool tf32 = prec == TLNN_PREC_TF32;
+    const int mode = tf32 ? EPI_GENERIC : pick_mode(ep, N);
+    // output tensor map of the epilogues that leave through TMA: 32 rows x 128 bytes (64 bf16 or 32 float32 columns)
+    CUtensorMap ta, tb, to;
+    memset(&to, 0, sizeof(to));
+    if (mode == EPI_BF16 || mode == EPI_BF16_GELU) TL_TRY(make_tile_map(&to, true, ep.out, M, N, ep.ldo, 32));
+    if (mode == EPI_F32_ACCUM) TL_TRY(make_tile_map(&to, false, ep.out, M, N, ep.ldo, 32));
     if (use_pair(ctx->sm_count, prec, M, N)) {
-        CUtensorMap ta, tb;
         TL_TRY(make_tile_map(&ta, true, a, M, K, lda, BM));
         TL_TRY(make_tile_map(&tb, true, w, N, K, ldw, PairCfg::BN / 2));
-        return launch_pair_mode(ctx, pick_mode(ep, N), ta, tb, ep, M, N, K);
+        return launch_pair_mode(ctx, mode, ta, tb, to, ep, M, N, K);
     }
     const int bn = pick_bn(M, N, ctx->sm_count);
-    CUtensorMap ta, tb;
     TL_TRY(make_tile_map(&ta, prec == TLNN_PREC_BF16, a, M, K, lda, BM));
     TL_TRY(make_tile_map(&tb, prec == TLNN_PREC_BF16, w, N, K, ldw, bn));
-    const bool tf32 = prec == TLNN_PREC_TF32;
-    const int mode = pick_mode(ep, N);
-    if (bn == 256) return launch_bn<256>(ctx, tf32, mode, ta, tb, ep, M, N, K);
-    if (bn == 128) return launch_bn<128>(ctx, tf32, mode, ta, tb, ep, M, N, K);
-    return launch_bn<64>(ctx, tf32, mode, ta, tb, ep, M, N, K);
+    if (bn == 256) return launch_bn<256>(ctx, tf32, mode, ta, tb, to, ep, M, N, K);
+    if (bn == 128) return launch_bn<128>(ctx, tf32, mode, ta, tb, to, ep, M, N, K);
+    return launch_bn<64>(ctx, tf32, mode, ta, tb, to, ep, M, N, K);
 }
 
 // ---- tensor-map encoding (shared with the attention kernel) ---------------------------------------------------------

@@ -64,7 +64,10 @@ int run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* 
     void* a = cur.take<char>((size_t)M * d * op_size(prec));
     void* qkv = cur.take<char>((size_t)M * 3 * d * op_size(prec));
     void* att = cur.take<char>((size_t)M * d * op_size(prec));
-    float* y = cur.take<float>((size_t)M * d);
+    // out == x: the caller owns x and wants the block applied in place.  Both residual additions then accumulate into
+    // x itself (the GEMM adds its tile to the buffer through the memory system), and no second stream buffer is needed.
+    const bool in_place = out == x;
+    float* y = in_place ? out : cur.take<float>((size_t)M * d);
     void* hid = cur.take<char>((size_t)M * 4 * d * op_size(prec));
 
     TL_TRY(tl_layernorm(ctx, x, p->ln1_gamma, p->ln1_beta, 1e-5f, a, kind, M, d));
@@ -325,8 +328,12 @@ extern "C" int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const vo
     float* xb = cur.take<float>((size_t)M * d);
     TL_TRY(tl_embed(ctx, ids, ids_type, m->tok_table, m->pos_table, xa, B, T, d, m->vocab));
     for (int l = 0; l < m->layers; l++) {
-        TL_TRY(run_block(ctx, m->prec, xa, &m->blocks[l], m->act, xb, B, T, d, m->heads, 1, cur));
-        float* t = xa; xa = xb; xb = t;
+        if (m->prec == TLNN_PREC_BF16) {
+            TL_TRY(run_block(ctx, m->prec, xa, &m->blocks[l], m->act, xa, B, T, d, m->heads, 1, cur));     // in place
+        } else {
+            TL_TRY(run_block(ctx, m->prec, xa, &m->blocks[l], m->act, xb, B, T, d, m->heads, 1, cur));
+            float* t = xa; xa = xb; xb = t;
+        }
     }
     void* a = cur.take<char>((size_t)M * d * op_size(m->prec));
     TL_TRY(tl_layernorm(ctx, xa, m->lnf_gamma, m->lnf_beta, 1e-5f, a, op_kind(m->prec), M, d));
