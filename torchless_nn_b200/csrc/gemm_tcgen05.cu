@@ -84,16 +84,34 @@ __device__ __forceinline__ float apply_act(int act, float v) {
 template <bool ACCURATE>
 __device__ __forceinline__ void apply_act_chunk(int act, float (&v)[32]) {
     if (act == TLNN_ACT_GELU) {
+        if (ACCURATE) {
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const float x = v[j];
-            if (ACCURATE) {
+            for (int j = 0; j < 32; j++) {
+                const float x = v[j];
                 const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
                 v[j] = 0.5f * x * (1.f + tanhf(u));
-            } else {
-                const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
-                const float h = 0.5f * x;
-                v[j] = fmaf(h, tanh_fast(u), h);
+            }
+        } else {
+            // 0.5 x (1 + tanh(x (c0 + c1 x^2))) on pairs of float32 (mul / fma .f32x2): five packed instructions and
+            // two hardware tanh per pair
+            uint64_t c0, c1, half2;
+            asm("mov.b64 %0, {%1, %1};" : "=l"(c0) : "f"(0.7978845608f));
+            asm("mov.b64 %0, {%1, %1};" : "=l"(c1) : "f"(0.0356774081f));
+            asm("mov.b64 %0, {%1, %1};" : "=l"(half2) : "f"(0.5f));
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                uint64_t x, x2, w, u, h, t, r;
+                float u0, u1;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(v[j]), "f"(v[j + 1]));
+                asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(x2) : "l"(x));
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(w) : "l"(x2), "l"(c1), "l"(c0));
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(u) : "l"(x), "l"(w));
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(h) : "l"(x), "l"(half2));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(u0), "=f"(u1) : "l"(u));
+                const float t0 = tanh_fast(u0), t1 = tanh_fast(u1);
+                asm("mov.b64 %0, {%1, %2};" : "=l"(t) : "f"(t0), "f"(t1));
+                asm("fma.rn.f32x2 %0, %1, %2, %1;" : "=l"(r) : "l"(h), "l"(t));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(v[j]), "=f"(v[j + 1]) : "l"(r));
             }
         }
     } else if (act == TLNN_ACT_SILU) {
