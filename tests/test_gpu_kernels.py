@@ -40,6 +40,40 @@ def test_dense_matches_numpy(engine, prec, M, K, N):
     assert rel_err(y, ref) < TOL[prec]
 
 
+@pytest.mark.parametrize("M,K,N", [(10240, 256, 1024), (9999, 192, 1184), (12800, 64, 800)])
+def test_dense_many_tiles_pair_kernel(engine, M, K, N):
+    """Shapes with at least as many 256 x 256 tiles as SMs take the CTA-pair GEMM in bf16 mode (ragged M, ragged N)."""
+    from torchless_nn_b200.layers import Dense
+    engine.set_precision("bf16")
+    try:
+        rng = np.random.default_rng(M + K + N)
+        w = (rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)).astype(np.float32)
+        b = rng.standard_normal(N, dtype=np.float32)
+        x = rng.standard_normal((M, K), dtype=np.float32)
+        layer = Dense(K, N)
+        _load(w, layer.weights)
+        _load(b, layer.bias)
+        y = layer.forward(x).get()
+        ref = x @ w + b
+        assert rel_err(y, ref) < TOL["bf16"]
+    finally:
+        engine.set_precision("tf32")
+
+
+def test_suite_with_pair_kernel_forced():
+    """TLNN_GEMM_PAIR=force routes every bf16 product through the CTA-pair kernel: the layer tests must still pass."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, TLNN_GEMM_PAIR="force")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        os.path.join(root, "tests", "test_gpu_kernels.py"),
+                        "-k", "dense_matches_numpy or ffn_golden or block_golden or attention_golden"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_dense_golden(engine, prec, golden):
     from torchless_nn_b200.layers import Dense
     g = golden("layers")
@@ -178,17 +212,19 @@ def test_attention_golden(engine, prec, golden, tag):
 
 
 @pytest.mark.parametrize("B,T,d,H,causal", [(2, 300, 128, 2, True), (1, 257, 256, 2, False), (3, 64, 64, 2, True),
-                                            (1, 1024, 128, 2, True), (2, 129, 256, 2, True)])
+                                            (1, 1024, 128, 2, True), (2, 129, 256, 2, True),
+                                            (4, 512, 256, 4, True), (1, 2048, 64, 1, True), (5, 193, 128, 2, False),
+                                            (2, 1000, 192, 3, True), (37, 200, 64, 1, True)])
 def test_attention_long_and_ragged(engine, prec, B, T, d, H, causal):
     from torchless_nn_b200.layers import MultiHeadAttention
     rng = np.random.default_rng(T + d)
-    at = MultiHeadAttention(d, 1024, H, decoder=causal)
+    at = MultiHeadAttention(d, max(1024, T), H, decoder=causal)
     ws = [rng.standard_normal(p.shape, dtype=np.float32) * np.float32(0.08) for p in at.parameters]
     for p, w in zip(at.parameters, ws):
         _load(w, p)
     x = rng.standard_normal((B, T, d), dtype=np.float32)
     y = at.forward(x).get()
-    ref = onp.attention(x, *ws, H, onp.causal_mask(1024) if causal else None)
+    ref = onp.attention(x, *ws, H, onp.causal_mask(max(1024, T)) if causal else None)
     assert rel_err(y, ref) < TOL[prec]
 
 

@@ -38,6 +38,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware keep the thread suspended for up to `ns` nanoseconds (it wakes as soon as the
+// phase completes): a waiting role then executes almost no instructions instead of polling.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Non-blocking probe of a phase (try_wait may suspend the thread for a while; a thread that serves several barriers
 // polls with this instead).
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -52,6 +66,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+#ifndef TLNN_WAIT_HINT_NS
+#define TLNN_WAIT_HINT_NS 20000u
+#endif
 // Bounded wait.  Returns false (after recording the failure and raising the CTA's abort flag) when the barrier
 // did not flip within WAIT_LIMIT_NS or another role of this CTA already gave up.
 // (Kept out of line unless TLNN_INLINE_WAITS is defined: a kernel that re-partitions registers with setmaxnreg cannot
@@ -66,7 +83,7 @@ static __device__ __noinline__ bool mbar_wait_slow(
     unsigned long long t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 128; i++)
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait_hint(bar, parity, TLNN_WAIT_HINT_NS)) return true;
         if (*abort_flag) return false;
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
             *abort_flag = 1;
