@@ -38,7 +38,7 @@ template <int BN> struct Cfg {
     static constexpr uint32_t B_BYTES = BN * ROW_BYTES;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr uint32_t BAR_BYTES = 1024;      // keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
+    static constexpr uint32_t BAR_BYTES = 2048;      // barriers, then eight 128-byte bias lines; keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
     static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;     // eight 4 KB staging tiles
     static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024 /*alignment slack*/;
 };
@@ -189,6 +189,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     const int quarter = warp & 3;
     const int half = ew >> 2;                       // 0: even chunks, 1: odd chunks
     float* stage_tile = staging + ew * 1024;
+    float* bias_line = staging - 256 + ew * 32;          // eight 128-byte lines in the 1 KB below the staging tiles
     const int sub_row = lane >> 3;                  // phase 2: row inside a group of four
     const int c4 = lane & 7;                        // phase 2: 16-byte unit inside the 128-byte row segment
 
@@ -231,8 +232,13 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
             const bool full = ncols == 32;
             const bool fast = vec_ok && full;
             // requests that do not depend on the accumulator go out first
-            float bias_lane = 0.f;
-            if (has_bias && lane < ncols) bias_lane = __ldg(ep.bias + col0 + lane);
+            // the chunk's 32 bias values go through a 128-byte line of shared memory: every thread (= row) needs all of
+            // them, and eight broadcast reads are cheaper than 32 shuffles
+            if (has_bias) {
+                __syncwarp();                                  // the previous chunk's reads are done
+                bias_line[lane] = lane < ncols ? __ldg(ep.bias + col0 + lane) : 0.f;
+                __syncwarp();
+            }
             float4 res[8];
             if (has_res && fast) {
 #pragma unroll
@@ -271,7 +277,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
             // ---- phase 1
             if (has_bias) {
 #pragma unroll
-                for (int j = 0; j < 32; j++) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
+                for (int u = 0; u < 8; u++) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bias_line + 4 * u);
+                    v[4 * u] += b4.x; v[4 * u + 1] += b4.y; v[4 * u + 2] += b4.z; v[4 * u + 3] += b4.w;
+                }
             }
             if (MODE == EPI_BF16_GELU) {
                 apply_act_chunk<false>(TLNN_ACT_GELU, v);
@@ -532,7 +541,7 @@ struct PairCfg {
     static constexpr uint32_t B_BYTES = (BN / 2) * ROW_BYTES;      // 16 KB: this CTA's half of the W tile
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = PAIR_TMEM_COLS;
-    static constexpr uint32_t BAR_BYTES = 1024;      // keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
+    static constexpr uint32_t BAR_BYTES = 2048;      // barriers, then eight 128-byte bias lines; keeps the staging tiles 1024-byte aligned (TMA swizzle phase)
     static constexpr uint32_t EPI_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
     static constexpr size_t SMEM = (size_t)EPI_OFFSET + 8 * 4096 + 1024;
 };
