@@ -333,6 +333,101 @@ attention_f32_kernel(const float* __restrict__ qkv, float* __restrict__ out, int
     }
 }
 
+// Float32 attention, one thread per query (head dimension 32 or 64).  The query row, the running maximum, the row sum
+// and the output row live in registers; key and value rows are read from shared memory as broadcasts (every thread of
+// a warp reads the same 16 bytes), so a key costs 2 HD / 4 shared loads per thread for 2 HD multiply-adds and nothing
+// is exchanged between threads.  Keys are taken eight at a time: eight scores, one maximum update and one rescale of
+// the output row, then eight exponentials.  Exact float32 arithmetic and libm-grade expf keep the 2e-3 budget of the
+// float32 / TF32 mode.
+template <int HD, bool CAUSAL>
+__global__ void __launch_bounds__(128)
+attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict__ out, int T, int H, float inv_sqrt_hd,
+                               int round_out) {
+    constexpr int KT = 64;                         // keys per shared-memory tile
+    constexpr int V4 = HD / 4;
+    __shared__ __align__(16) float sK[KT][HD];
+    __shared__ __align__(16) float sV[KT][HD];
+
+    const int d = H * HD;
+    const long long row_stride = 3ll * d;
+    const int bh = blockIdx.y, b = bh / H, h = bh % H;
+    const int q0 = blockIdx.x * blockDim.x;
+    const int qi = q0 + threadIdx.x;
+    const bool active = qi < T;
+    const float* qbase = qkv + (long long)b * T * row_stride + h * HD;
+    const float* kbase = qbase + d;
+    const float* vbase = qbase + 2 * d;
+
+    float q[HD], o[HD];
+#pragma unroll
+    for (int c = 0; c < V4; c++) {
+        const float4 t = active ? *reinterpret_cast<const float4*>(qbase + (long long)qi * row_stride + 4 * c)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        q[4 * c] = t.x; q[4 * c + 1] = t.y; q[4 * c + 2] = t.z; q[4 * c + 3] = t.w;
+        o[4 * c] = 0.f; o[4 * c + 1] = 0.f; o[4 * c + 2] = 0.f; o[4 * c + 3] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    const int kv_end = CAUSAL ? min(T, q0 + (int)blockDim.x) : T;
+    for (int k0 = 0; k0 < kv_end; k0 += KT) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < KT * V4; i += blockDim.x) {
+            const int r = i / V4, c = i % V4;
+            const bool ok = k0 + r < T;
+            const long long off = (long long)(k0 + r) * row_stride + 4 * c;
+            *reinterpret_cast<float4*>(&sK[r][4 * c]) = ok ? *reinterpret_cast<const float4*>(kbase + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(&sV[r][4 * c]) = ok ? *reinterpret_cast<const float4*>(vbase + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncthreads();
+        if (!active) continue;
+        const int nk = min(KT, kv_end - k0);
+        for (int c0 = 0; c0 < nk; c0 += 8) {
+            if (CAUSAL && k0 + c0 > qi) break;                     // every later key is masked for this query
+            float sc[8];
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int c = 0; c < V4; c++) {
+                    const float4 kv = *reinterpret_cast<const float4*>(&sK[c0 + kk][4 * c]);
+                    a0 = fmaf(q[4 * c], kv.x, a0); a1 = fmaf(q[4 * c + 1], kv.y, a1);
+                    a2 = fmaf(q[4 * c + 2], kv.z, a2); a3 = fmaf(q[4 * c + 3], kv.w, a3);
+                }
+                const int key = k0 + c0 + kk;
+                const bool live = key < T && (!CAUSAL || key <= qi);
+                sc[kk] = live ? ((a0 + a1) + (a2 + a3)) * inv_sqrt_hd : -INFINITY;
+            }
+            float cm = fmaxf(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])), fmaxf(fmaxf(sc[4], sc[5]), fmaxf(sc[6], sc[7])));
+            const float mn = fmaxf(m, cm);
+            if (mn == -INFINITY) continue;                          // nothing visible yet
+            const float alpha = expf(m - mn);                        // 0 while m is still -inf
+            l *= alpha;
+#pragma unroll
+            for (int c = 0; c < HD; c++) o[c] *= alpha;
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                const float p = expf(sc[kk] - mn);                   // 0 for masked keys
+                l += p;
+#pragma unroll
+                for (int c = 0; c < V4; c++) {
+                    const float4 vv = *reinterpret_cast<const float4*>(&sV[c0 + kk][4 * c]);
+                    o[4 * c] = fmaf(p, vv.x, o[4 * c]); o[4 * c + 1] = fmaf(p, vv.y, o[4 * c + 1]);
+                    o[4 * c + 2] = fmaf(p, vv.z, o[4 * c + 2]); o[4 * c + 3] = fmaf(p, vv.w, o[4 * c + 3]);
+                }
+            }
+            m = mn;
+        }
+    }
+    if (active) {
+        float* op = out + ((long long)b * T + qi) * d + h * HD;
+#pragma unroll
+        for (int c = 0; c < V4; c++) {
+            float4 r = make_float4(o[4 * c] / l, o[4 * c + 1] / l, o[4 * c + 2] / l, o[4 * c + 3] / l);
+            if (round_out) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
+            *reinterpret_cast<float4*>(op + 4 * c) = r;
+        }
+    }
+}
+
 template <int HD>
 int launch_bf16(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16* out, int B, int T, int H, int causal) {
     const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HD * 2;
@@ -354,8 +449,20 @@ int launch_bf16(tlnn_ctx* ctx, const __nv_bfloat16* qkv, __nv_bfloat16* out, int
 
 template <int HD>
 int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H, int causal, int round_out) {
-    dim3 grid((T + F32_QPB - 1) / F32_QPB, B * H);
     const float inv = 1.f / sqrtf((float)HD);
+    if constexpr (HD <= 64) {
+        // the packed projection rows must allow 16-byte loads of a head's slice
+        if ((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+            const int threads = T >= 128 ? 128 : ((T + 31) / 32) * 32;
+            dim3 grid((T + threads - 1) / threads, B * H);
+            if (causal)
+                TL_LAUNCH(ctx, "attention_f32_causal", attention_f32_rowthread_kernel<HD, true><<<grid, threads, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
+            else
+                TL_LAUNCH(ctx, "attention_f32_full", attention_f32_rowthread_kernel<HD, false><<<grid, threads, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
+            return TLNN_OK;
+        }
+    }
+    dim3 grid((T + F32_QPB - 1) / F32_QPB, B * H);
     if (causal)
         TL_LAUNCH(ctx, "attention_f32_causal", attention_f32_kernel<HD, true><<<grid, 128, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
     else
