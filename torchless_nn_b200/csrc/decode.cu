@@ -255,16 +255,20 @@ int decode_one(tlnn_decoder* dec) {
         TL_TRY(tl_gemm(ctx, prec, dec->a, d, p.wqkv_t, d, B, 3 * d, d, e1));
         TL_TRY(launch_decode_attention(dec, l));
         tl_gemm_epilogue e2;
-        e2.bias = p.bo; e2.residual = x; e2.ldr = d; e2.out = dec->y; e2.ldo = d; e2.out_kind = TL_OUT_F32;
+        // bf16 mode keeps the residual stream in place: x += attention projection, x += feed-forward (the GEMM adds its
+        // tiles into x, split over K ranges when there are few tiles)
+        float* y = prec == TLNN_PREC_BF16 ? x : dec->y;
+        e2.bias = p.bo; e2.residual = x; e2.ldr = d; e2.out = y; e2.ldo = d; e2.out_kind = TL_OUT_F32;
         TL_TRY(tl_gemm(ctx, prec, dec->att, d, p.wo_t, d, B, d, d, e2));
-        TL_TRY(tl_layernorm(ctx, dec->y, p.ln2_gamma, p.ln2_beta, 1e-5f, dec->a, kind, B, d));
+        TL_TRY(tl_layernorm(ctx, y, p.ln2_gamma, p.ln2_beta, 1e-5f, dec->a, kind, B, d));
         tl_gemm_epilogue e3;
         e3.bias = p.b1; e3.act = m.act; e3.accurate_math = prec == TLNN_PREC_TF32; e3.out = dec->hid; e3.ldo = 4 * d; e3.out_kind = kind;
         TL_TRY(tl_gemm(ctx, prec, dec->a, d, p.w1_t, d, B, 4 * d, d, e3));
         tl_gemm_epilogue e4;
-        e4.bias = p.b2; e4.residual = dec->y; e4.ldr = d; e4.out = xn; e4.ldo = d; e4.out_kind = TL_OUT_F32;
+        float* out = prec == TLNN_PREC_BF16 ? x : xn;
+        e4.bias = p.b2; e4.residual = y; e4.ldr = d; e4.out = out; e4.ldo = d; e4.out_kind = TL_OUT_F32;
         TL_TRY(tl_gemm(ctx, prec, dec->hid, 4 * d, p.w2_t, 4 * d, B, d, 4 * d, e4));
-        float* t = x; x = xn; xn = t;
+        if (prec != TLNN_PREC_BF16) { float* t = x; x = xn; xn = t; }
     }
     TL_TRY(tl_layernorm(ctx, x, m.lnf_gamma, m.lnf_beta, 1e-5f, dec->a, kind, B, d));
     tl_gemm_epilogue eh;

@@ -171,7 +171,7 @@ template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M, int N, int m_tiles, int n_tiles,
                                               int total_tiles, int warp, int lane, uint32_t tmem_base, float* staging,
                                               uint64_t* acc_full, uint64_t* acc_empty, volatile int* abort_flag,
-                                              tlnn_dev_err* err, const CUtensorMap* tm_out) {
+                                              tlnn_dev_err* err, const CUtensorMap* tm_out, int split_k = 1) {
     const int tile0 = PAIR ? (int)cluster_id_x() : (int)blockIdx.x;
     const int tile_step = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
     const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
@@ -207,7 +207,11 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     }
 
     int local = 0;
-    for (int t = tile0; t < total_tiles; t += tile_step, local++) {
+    // with split_k > 1 (in-place accumulation only) a work unit is one K range of one tile; the ranges of a tile add
+    // their partial sums into the output independently, and only range 0 adds the bias
+    for (int u = tile0; u < total_tiles * split_k; u += tile_step, local++) {
+        const int t = u / split_k;
+        const bool first_split = u - t * split_k == 0;
         TileCoord tc = tile_coord(t, m_tiles, n_tiles);
         if (PAIR) tc.m_blk = tc.m_blk * 2 + cta_rank;
         const int buf = local & 1;
@@ -234,7 +238,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
             // requests that do not depend on the accumulator go out first
             // the chunk's 32 bias values go through a 128-byte line of shared memory: every thread (= row) needs all of
             // them, and eight broadcast reads are cheaper than 32 shuffles
-            if (has_bias) {
+            if (has_bias && first_split) {
                 __syncwarp();                                  // the previous chunk's reads are done
                 bias_line[lane] = lane < ncols ? __ldg(ep.bias + col0 + lane) : 0.f;
                 __syncwarp();
@@ -275,7 +279,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = __uint_as_float(acc[j]);
             // ---- phase 1
-            if (has_bias) {
+            if (has_bias && first_split) {
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
                     const float4 b4 = *reinterpret_cast<const float4*>(bias_line + 4 * u);
@@ -414,7 +418,7 @@ template <int BN, bool TF32, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmOut, const tl_gemm_epilogue ep, int M, int N, int K, int m_tiles,
-                    int n_tiles, tlnn_dev_err* err) {
+                    int n_tiles, int split_k, tlnn_dev_err* err) {
     using C = Cfg<BN>;
     constexpr int STAGES = C::STAGES;
     constexpr int K_ELEMS = TF32 ? 32 : 64;       // elements per 128-byte row
@@ -432,6 +436,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int lane = threadIdx.x & 31;
     const int total_tiles = m_tiles * n_tiles;
     const int num_k = (K + K_ELEMS - 1) / K_ELEMS;
+    const int kb_per_split = (num_k + split_k - 1) / split_k;      // the host guarantees that no K range is empty
+    const int total_units = total_tiles * split_k;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
@@ -465,9 +471,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const int t = u / split_k;
+                const int kb_lo = (u - t * split_k) * kb_per_split, kb_hi = min(num_k, kb_lo + kb_per_split);
                 TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-                for (int kb = 0; kb < num_k; kb++) {
+                for (int kb = kb_lo; kb < kb_hi; kb++) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, err, 101)) { ok = false; break; }
                     uint32_t sa = smem_u32(smem + (size_t)stage * C::STAGE_BYTES);
                     uint32_t bar = smem_u32(&full_bar[stage]);
@@ -486,13 +494,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, local++) {
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, local++) {
+                const int kb_lo = (u % split_k) * kb_per_split, kb_hi = min(num_k, kb_lo + kb_per_split);
                 const int buf = local & 1;
                 const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
                 if (!mbar_wait(&acc_empty[buf], buf_phase ^ 1u, abort_flag, err, 102)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < num_k; kb++) {
+                for (int kb = kb_lo; kb < kb_hi; kb++) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag, err, 103)) { ok = false; break; }
                     tc_fence_after();
                     uint32_t sa = smem_u32(smem + (size_t)stage * C::STAGE_BYTES);
@@ -502,7 +511,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int k = 0; k < ROW_BYTES / MMA_K_BYTES; k++) {
                         // advancing K inside the swizzle atom = advancing the start address by 32 bytes (>>4 = 2)
                         umma<TF32>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                                   (kb | k) != 0 ? 1u : 0u);
+                                   (kb != kb_lo || k != 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -513,7 +522,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else {
         // ------------------------------------------------------------------ epilogue (8 warps, 128 rows x BN columns)
         epilogue_warp<BN, MODE>(ep, M, N, m_tiles, n_tiles, total_tiles, warp, lane, tmem_base,
-                                reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err, &tmOut);
+                                reinterpret_cast<float*>(smem + C::EPI_OFFSET), acc_full, acc_empty, abort_flag, err, &tmOut,
+                                split_k);
     }
 
     tc_fence_before();
@@ -700,13 +710,28 @@ int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CU
     auto kernel = gemm_tcgen05_kernel<BN, TF32, MODE>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM));
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-    const long long total = (long long)m_tiles * n_tiles;
+    long long total = (long long)m_tiles * n_tiles;
     TL_REQUIRE(total < (1ll << 31), "gemm: too many tiles");
+    // In-place accumulation with few tiles and a long contraction (the feed-forward output and attention output
+    // products of a decode step): split K over several CTAs, each adding its partial tile into the output.  The order
+    // of those float32 additions is not fixed from run to run.
+    int split_k = 1;
+    static const bool split_allowed = !(getenv("TLNN_GEMM_SPLITK") && strcmp(getenv("TLNN_GEMM_SPLITK"), "0") == 0);
+    if (MODE == EPI_F32_ACCUM && split_allowed && total * 2 <= ctx->sm_count) {
+        const int num_k = (K + (TF32 ? 32 : 64) - 1) / (TF32 ? 32 : 64);
+        int want = (int)(ctx->sm_count / total);
+        if (want > num_k / 3) want = num_k / 3;                 // at least three k-blocks per range
+        if (want > 1) {
+            const int per = (num_k + want - 1) / want;
+            split_k = (num_k + per - 1) / per;                   // no empty range
+        }
+    }
+    total *= split_k;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     const char* name = TF32 ? (BN == 256 ? "gemm_tf32_n256" : BN == 128 ? "gemm_tf32_n128" : "gemm_tf32_n64")
                             : (BN == 256 ? "gemm_bf16_n256" : BN == 128 ? "gemm_bf16_n128" : "gemm_bf16_n64");
     TL_LAUNCH(ctx, name, kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM, ctx->stream>>>(ta, tb, to, ep, M, N, K, m_tiles, n_tiles,
-                                                                                   ctx->d_err));
+                                                                                   split_k, ctx->d_err));
     return TLNN_OK;
 }
 
