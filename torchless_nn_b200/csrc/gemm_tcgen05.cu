@@ -793,7 +793,8 @@ bool use_pair(int sm_count, int prec, int M, int N) {
     if (prec != TLNN_PREC_BF16 || policy == 0) return false;
     if (policy == 2) return true;
     const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + PairCfg::BN - 1) / PairCfg::BN);
-    return pick_bn(M, N, sm_count) == 256 && tiles >= (long long)sm_count;
+    // a pair needs rows for both of its CTAs
+    return M > BM && pick_bn(M, N, sm_count) == 256 && tiles >= (long long)sm_count;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
