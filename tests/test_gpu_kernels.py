@@ -60,6 +60,33 @@ def test_dense_many_tiles_pair_kernel(engine, M, K, N):
         engine.set_precision("tf32")
 
 
+@pytest.mark.parametrize("M,K,N", [(64, 768, 768), (64, 3072, 768), (100, 1024, 256), (10240, 256, 1024), (300, 128, 384)])
+def test_linear_in_place_residual(engine, M, K, N):
+    """residual == out: the product is added to the buffer in place (TMA reduce-add epilogue in bf16 mode; with few
+    tiles the contraction is split over several CTAs).  Through the C ABI, against NumPy."""
+    import ctypes as C
+    from torchless_nn_b200 import _lib, backend
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.device_array import DeviceArray
+    from torchless_nn_b200.utils import PreparedWeight
+    engine.set_precision("bf16")
+    try:
+        rng = np.random.default_rng(M * 3 + K + N)
+        w = (rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)).astype(np.float32)
+        b = rng.standard_normal(N, dtype=np.float32)
+        a = rng.standard_normal((M, K), dtype=np.float32)
+        x = rng.standard_normal((M, N), dtype=np.float32)
+        wd, bd, ad, xd = (DeviceArray.from_numpy(v) for v in (w, b, a, x))
+        pw = PreparedWeight(wd, transpose=True)
+        for _ in range(2):                      # twice: x += a w + b, then once more on the result
+            check(lib.tlnn_linear_fwd(backend.ctx(), backend.precision_code(), ad.ptr, K, pw.ptr(), bd.ptr, _lib.ACT_NONE,
+                                      xd.ptr, N, xd.ptr, N, M, N, K))
+        ref = x + 2.0 * (a @ w + b)
+        assert rel_err(xd.get(), ref) < TOL["bf16"]
+    finally:
+        engine.set_precision("tf32")
+
+
 def test_suite_with_pair_kernel_forced():
     """TLNN_GEMM_PAIR=force routes every bf16 product through the CTA-pair kernel: the layer tests must still pass."""
     import os
