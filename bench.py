@@ -71,7 +71,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except Exception:
@@ -79,7 +79,12 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark(self):
+        """Only samples taken after this call count (the sampler is started early because nvidia-smi takes a
+        moment to deliver its first line)."""
+        self.since = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -91,7 +96,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        since = getattr(self, "since", 0.0)
+        for stamp, ln in self.lines:
+            if stamp < since:
+                continue
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -268,16 +276,17 @@ def run_b200(args, spec):
         return float(t.item())
 
     # ---- device-resident throughput ---------------------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        step_resident()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
     check(lib.tlnn_prof_classes(ctx, 1))
     backend.launch_count(reset=True)
     ms = C.c_float()
     barrier()
+    sampler.mark()                     # clocks are counted from here to the end of the timed region
     check(lib.tlnn_prof_begin(ctx))
     for _ in range(args.steps):
         step_resident()
