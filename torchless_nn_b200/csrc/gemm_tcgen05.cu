@@ -150,9 +150,10 @@ enum {
     EPI_BF16_GELU = 2,   // bf16 out, bias, tanh-GeLU (hardware tanh)  same conditions
     EPI_F32_RES = 3,     // float32 out (+bias) + float32 residual     same conditions, residual rows aligned too
     EPI_ARGMAX = 4,      // no output, (+bias), per-row arg-max candidates; ragged N allowed
-    EPI_F32_ACCUM = 5    // out += acc (+bias): the residual IS the output buffer (in-place residual stream)
+    EPI_F32_ACCUM = 5,   // out += acc (+bias): the residual IS the output buffer (in-place residual stream)
+    EPI_F32 = 6          // float32 out (+bias), no activation, no residual
 };
-// EPI_BF16, EPI_BF16_GELU and EPI_F32_ACCUM leave the tile through TMA: the warp writes its 32-row slab into its
+// EPI_BF16, EPI_BF16_GELU, EPI_F32 and EPI_F32_ACCUM leave the tile through TMA: the warp writes its 32-row slab into its
 // staging tile in the 128-byte-swizzled layout and one lane issues a bulk tensor store (bf16: 64 columns at a time) or a
 // bulk tensor reduce-add (float32: the memory system adds the tile to the residual in place, so the residual never
 // travels to the SM).  No per-thread global loads or stores, no second pass over the staging tile.
@@ -184,7 +185,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     constexpr bool GENERIC = MODE == EPI_GENERIC;
     constexpr bool HAS_OUT = MODE != EPI_ARGMAX;
     constexpr bool TMA_BF16 = MODE == EPI_BF16 || MODE == EPI_BF16_GELU;
-    constexpr bool TMA_OUT = TMA_BF16 || MODE == EPI_F32_ACCUM;
+    constexpr bool TMA_OUT = TMA_BF16 || MODE == EPI_F32_ACCUM || MODE == EPI_F32;
     const int ew = warp - 2;                        // 0..7
     const int quarter = warp & 3;
     const int half = ew >> 2;                       // 0: even chunks, 1: odd chunks
@@ -328,8 +329,8 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                     __syncwarp();
                     if (lane == 0) {
                         const int x0 = TMA_BF16 ? n0 + (chunk & ~1) * 32 : col0;
-                        if (TMA_BF16) tma_store_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
-                        else tma_reduce_add_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
+                        if (MODE == EPI_F32_ACCUM) tma_reduce_add_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
+                        else tma_store_2d(tm_out, smem_u32(stage_tile), x0, (int)row_base);
                         tma_store_commit();
                     }
                 }
@@ -442,7 +443,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM) tma_prefetch_desc(&tmOut);
+        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM || MODE == EPI_F32) tma_prefetch_desc(&tmOut);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
@@ -586,7 +587,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM) tma_prefetch_desc(&tmOut);
+        if (MODE == EPI_BF16 || MODE == EPI_BF16_GELU || MODE == EPI_F32_ACCUM || MODE == EPI_F32) tma_prefetch_desc(&tmOut);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
@@ -776,6 +777,7 @@ int launch_pair_mode(tlnn_ctx* ctx, int mode, const CUtensorMap& ta, const CUten
         case EPI_BF16_GELU: return launch_pair<EPI_BF16_GELU>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_F32_RES: return launch_pair<EPI_F32_RES>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_F32_ACCUM: return launch_pair<EPI_F32_ACCUM>(ctx, ta, tb, to, ep, M, N, K);
+        case EPI_F32: return launch_pair<EPI_F32>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_ARGMAX: return launch_pair<EPI_ARGMAX>(ctx, ta, tb, to, ep, M, N, K);
         default: return launch_pair<EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);
     }
@@ -810,6 +812,8 @@ int pick_mode(const tl_gemm_epilogue& ep, int N) {
         if (ep.act == TLNN_ACT_NONE) return EPI_BF16;
         if (ep.act == TLNN_ACT_GELU && !ep.accurate_math) return EPI_BF16_GELU;
     }
+    if (ep.out_kind == TL_OUT_F32 && ep.residual == nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0)
+        return EPI_F32;
     if (ep.out_kind == TL_OUT_F32 && ep.residual != nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0 &&
         aligned16(ep.residual) && ep.ldr % 4 == 0)
         return (ep.residual == ep.out && ep.ldr == ep.ldo) ? EPI_F32_ACCUM : EPI_F32_RES;
@@ -819,8 +823,16 @@ int pick_mode(const tl_gemm_epilogue& ep, int N) {
 template <int BN>
 int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
               const tl_gemm_epilogue& ep, int M, int N, int K) {
-    if (tf32) return launch<BN, true, EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);      // FP32/TF32 shapes are small
+    if (tf32) {
+        // float32 / TF32 operands: the variants whose output is plain float32
+        switch (mode) {
+            case EPI_F32: return launch<BN, true, EPI_F32>(ctx, ta, tb, to, ep, M, N, K);
+            case EPI_F32_RES: return launch<BN, true, EPI_F32_RES>(ctx, ta, tb, to, ep, M, N, K);
+            default: return launch<BN, true, EPI_GENERIC>(ctx, ta, tb, to, ep, M, N, K);
+        }
+    }
     switch (mode) {
+        case EPI_F32: return launch<BN, false, EPI_F32>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_BF16: return launch<BN, false, EPI_BF16>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_BF16_GELU: return launch<BN, false, EPI_BF16_GELU>(ctx, ta, tb, to, ep, M, N, K);
         case EPI_F32_RES: return launch<BN, false, EPI_F32_RES>(ctx, ta, tb, to, ep, M, N, K);
@@ -847,12 +859,13 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
     TL_REQUIRE((lda * esz) % 16 == 0 && (ldw * esz) % 16 == 0, "gemm: operand pitches must be multiples of 16 bytes");
     TL_REQUIRE(((uintptr_t)a & 15u) == 0 && ((uintptr_t)w & 15u) == 0, "gemm: operands must be 16-byte aligned");
     const bool tf32 = prec == TLNN_PREC_TF32;
-    const int mode = tf32 ? EPI_GENERIC : pick_mode(ep, N);
+    int mode = pick_mode(ep, N);
+    if (tf32 && mode != EPI_F32 && mode != EPI_F32_RES) mode = EPI_GENERIC;
     // output tensor map of the epilogues that leave through TMA: 32 rows x 128 bytes (64 bf16 or 32 float32 columns)
     CUtensorMap ta, tb, to;
     memset(&to, 0, sizeof(to));
     if (mode == EPI_BF16 || mode == EPI_BF16_GELU) TL_TRY(make_tile_map(&to, true, ep.out, M, N, ep.ldo, 32));
-    if (mode == EPI_F32_ACCUM) TL_TRY(make_tile_map(&to, false, ep.out, M, N, ep.ldo, 32));
+    if (mode == EPI_F32_ACCUM || mode == EPI_F32) TL_TRY(make_tile_map(&to, false, ep.out, M, N, ep.ldo, 32));
     if (use_pair(ctx->sm_count, prec, M, N)) {
         TL_TRY(make_tile_map(&ta, true, a, M, K, lda, BM));
         TL_TRY(make_tile_map(&tb, true, w, N, K, ldw, PairCfg::BN / 2));
