@@ -62,6 +62,7 @@ extern "C" int tlnn_shutdown(tlnn_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     for (auto& p : ctx->pending) { cudaEventDestroy(p.start); cudaEventDestroy(p.stop); }
     for (auto& e : ctx->event_pool) cudaEventDestroy(e);
+    tl_prefill_cache_free(ctx);
     if (ctx->ws) cudaFree(ctx->ws);
     cudaFree(ctx->d_err);
     cudaFree(ctx->d_sched);

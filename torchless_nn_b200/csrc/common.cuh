@@ -43,6 +43,7 @@ struct tlnn_ctx {
     tlnn_dev_err* h_err = nullptr;     // pinned host mirror
     int* d_sched = nullptr;            // device work counter of the persistent attention kernel (zeroed per launch)
     long long launches = 0;
+    void* prefill_cache = nullptr;     // captured graph of the last repeated tlnn_gpt_prefill call (layers.cu)
     // grow-only scratch arena used by the composite layer calls (stream-ordered reuse)
     char* ws = nullptr;
     size_t ws_bytes = 0;
@@ -98,6 +99,8 @@ int tl_launch_end(tlnn_ctx* ctx, const char* name);
         __VA_ARGS__;                         \
         TL_TRY(tl_launch_end(ctx, name));    \
     } while (0)
+
+void tl_prefill_cache_free(tlnn_ctx* ctx);     // layers.cu: drops the captured prefill graph
 
 // ---- scratch arena ---------------------------------------------------------------------------------
 // A composite call reserves its total need up front (which may reallocate while the stream is idle), then

@@ -303,26 +303,17 @@ extern "C" int tlnn_vit_head_fwd(tlnn_ctx* ctx, int prec, const float* x, const 
     return tlnn_linear_fwd(ctx, prec, x, (long long)T * d, w_t, bias, TLNN_ACT_NONE, nullptr, 0, out, n_out, B, n_out, d);
 }
 
-extern "C" int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T,
-                                float* logits, int32_t* tokens) {
-    TL_NOTNULL(ctx); TL_NOTNULL(m); TL_NOTNULL(m->tok_table); TL_NOTNULL(m->pos_table); TL_NOTNULL(m->blocks);
-    TL_NOTNULL(m->lnf_gamma); TL_NOTNULL(m->lnf_beta); TL_NOTNULL(m->head_t);
-    TL_REQUIRE(prec_ok(m->prec), "unknown precision %d", m->prec);
-    TL_REQUIRE(m->layers >= 0 && m->vocab > 0 && m->context > 0, "gpt_prefill: bad model description");
-    TL_REQUIRE(T <= m->context, "gpt_prefill: sequence length %d exceeds the context length %d", T, m->context);
-    TL_REQUIRE(ids_type == TLNN_I32 || ids_type == TLNN_I64 || ids_type == TLNN_U8, "token ids must be int32, int64 or uint8");
-    TL_REQUIRE(logits || tokens, "gpt_prefill: neither logits nor tokens requested");
-    TL_TRY(check_block_shape(B, T, m->d, m->heads));
-    for (int l = 0; l < m->layers; l++) TL_TRY(check_block_params(&m->blocks[l]));
+namespace {
+
+// Everything tlnn_gpt_prefill enqueues, given that the workspace is already reserved.
+int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T, float* logits,
+                    int32_t* tokens) {
     const long long M = (long long)B * T;
-    if (M == 0) return TLNN_OK;
-    TL_NOTNULL(ids);
-    TL_CUDA(cudaSetDevice(ctx->device));
     const int d = m->d;
     const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
     const size_t tail = block_ws_bytes(m->prec, M, d);
     const size_t head = head_ws_bytes(ctx, m->prec, M, d, m->vocab, tokens != nullptr);
-    TL_TRY(tl_ws_reserve(ctx, 2 * stream_bytes + (tail > head ? tail : head)));
+    if (ctx->ws_bytes < 2 * stream_bytes + (tail > head ? tail : head)) { tl_set_error("gpt_prefill: workspace not reserved"); return TLNN_ERR_VALUE; }
     tl_ws_cursor cur(ctx);
     float* xa = cur.take<float>((size_t)M * d);
     float* xb = cur.take<float>((size_t)M * d);
@@ -338,4 +329,109 @@ extern "C" int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const vo
     void* a = cur.take<char>((size_t)M * d * op_size(m->prec));
     TL_TRY(tl_layernorm(ctx, xa, m->lnf_gamma, m->lnf_beta, 1e-5f, a, op_kind(m->prec), M, d));
     return run_head(ctx, m->prec, a, m->head_t, m->head_bias, logits, tokens, M, d, m->vocab, cur);
+}
+
+// A repeated call (same model description, buffers and shape) replays a captured CUDA graph of the first repetition:
+// a step of a small shard is 172 kernels of tens of microseconds, and the gaps between plain launches add up.
+// TLNN_PREFILL_GRAPH=0 switches this off; per-class profiling always uses plain launches.
+struct prefill_cache {
+    tlnn_gpt_model m;
+    std::vector<tlnn_block_params> blocks;
+    const void* ids = nullptr;
+    int ids_type = 0, B = 0, T = 0;
+    float* logits = nullptr;
+    int32_t* tokens = nullptr;
+    char* ws = nullptr;
+    int seen = 0;                       // identical calls so far
+    long long launches = 0;             // kernels per replay
+    cudaGraphExec_t exec = nullptr;
+
+    bool matches(const tlnn_ctx* ctx, const tlnn_gpt_model* mm, const void* i, int it, int b, int t, float* lg, int32_t* tk) const {
+        if (ids != i || ids_type != it || B != b || T != t || logits != lg || tokens != tk || ws != ctx->ws) return false;
+        tlnn_gpt_model x = *mm, y = m;
+        x.blocks = nullptr; y.blocks = nullptr;
+        if (memcmp(&x, &y, sizeof(x)) != 0 || (int)blocks.size() != mm->layers) return false;
+        return mm->layers == 0 || memcmp(blocks.data(), mm->blocks, sizeof(tlnn_block_params) * blocks.size()) == 0;
+    }
+};
+
+bool prefill_graph_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("TLNN_PREFILL_GRAPH");
+        on = (e && strcmp(e, "0") == 0) ? 0 : 1;
+    }
+    return on == 1;
+}
+
+}  // namespace
+
+void tl_prefill_cache_free(tlnn_ctx* ctx) {
+    prefill_cache* c = static_cast<prefill_cache*>(ctx->prefill_cache);
+    if (!c) return;
+    if (c->exec) cudaGraphExecDestroy(c->exec);
+    delete c;
+    ctx->prefill_cache = nullptr;
+}
+
+extern "C" int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T,
+                                float* logits, int32_t* tokens) {
+    TL_NOTNULL(ctx); TL_NOTNULL(m); TL_NOTNULL(m->tok_table); TL_NOTNULL(m->pos_table); TL_NOTNULL(m->blocks);
+    TL_NOTNULL(m->lnf_gamma); TL_NOTNULL(m->lnf_beta); TL_NOTNULL(m->head_t);
+    TL_REQUIRE(prec_ok(m->prec), "unknown precision %d", m->prec);
+    TL_REQUIRE(m->layers >= 0 && m->vocab > 0 && m->context > 0, "gpt_prefill: bad model description");
+    TL_REQUIRE(T <= m->context, "gpt_prefill: sequence length %d exceeds the context length %d", T, m->context);
+    TL_REQUIRE(ids_type == TLNN_I32 || ids_type == TLNN_I64 || ids_type == TLNN_U8, "token ids must be int32, int64 or uint8");
+    TL_REQUIRE(logits || tokens, "gpt_prefill: neither logits nor tokens requested");
+    TL_TRY(check_block_shape(B, T, m->d, m->heads));
+    for (int l = 0; l < m->layers; l++) TL_TRY(check_block_params(&m->blocks[l]));
+    const long long M = (long long)B * T;
+    if (M == 0) return TLNN_OK;
+    TL_NOTNULL(ids);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    {
+        const int d = m->d;
+        const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
+        const size_t tail = block_ws_bytes(m->prec, M, d);
+        const size_t head = head_ws_bytes(ctx, m->prec, M, d, m->vocab, tokens != nullptr);
+        TL_TRY(tl_ws_reserve(ctx, 2 * stream_bytes + (tail > head ? tail : head)));
+    }
+    if (!prefill_graph_enabled() || ctx->prof_classes) return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+
+    prefill_cache* c = static_cast<prefill_cache*>(ctx->prefill_cache);
+    if (c && c->matches(ctx, m, ids, ids_type, B, T, logits, tokens)) {
+        if (c->exec) {
+            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
+            ctx->launches += c->launches;
+            return TLNN_OK;
+        }
+        if (++c->seen == 2) {
+            // second identical call: capture it, then run the capture
+            const long long before = ctx->launches;
+            TL_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            const int st = prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+            cudaGraph_t g = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
+            c->launches = ctx->launches - before;
+            ctx->launches = before;
+            if (st != TLNN_OK) { if (g) cudaGraphDestroy(g); return st; }
+            if (ce != cudaSuccess) return tl_cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
+            const cudaError_t ie = cudaGraphInstantiate(&c->exec, g, 0);
+            cudaGraphDestroy(g);
+            if (ie != cudaSuccess) { c->exec = nullptr; return tl_cuda_fail(ie, "cudaGraphInstantiate", __FILE__, __LINE__); }
+            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
+            ctx->launches += c->launches;
+            return TLNN_OK;
+        }
+        return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+    }
+    // a new description: remember it, run it with plain launches
+    tl_prefill_cache_free(ctx);
+    c = new prefill_cache();
+    c->m = *m;
+    c->blocks.assign(m->blocks, m->blocks + m->layers);
+    c->ids = ids; c->ids_type = ids_type; c->B = B; c->T = T; c->logits = logits; c->tokens = tokens; c->ws = ctx->ws;
+    c->seen = 1;
+    ctx->prefill_cache = c;
+    return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
 }
