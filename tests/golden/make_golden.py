@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by running the UNMODIFIED
 reference library (luke-skynet/torchless-nn) on its NumPy path.
 
-    XP_RUNTIME=CPU python tests/golden/make_golden.py --reference /path/to/torchless-nn [c1 c2 layers c3 c4 c5]
+    XP_RUNTIME=CPU python tests/golden/make_golden.py --reference /path/to/torchless-nn [c1 c2 layers c3 c4 c5 ckpt]
 
 The reference checkout is only needed to (re)generate fixtures; tests read the
 committed ``.npz`` files.  For each configuration the script builds the
@@ -293,6 +293,60 @@ def gen_layers(ref):
     print("layers:", len(out), "arrays")
 
 
+def notebook_helpers(reference_path, ref):
+    """``save_weights`` / ``load_weights`` as the reference's notebook defines them, executed from the checkout."""
+    import json
+    import pickle
+    nb = json.load(open(os.path.join(reference_path, "demo.ipynb")))
+    ns = {"pickle": pickle, "xp": np, "np": np}
+    for cell in nb["cells"]:
+        src = "".join(cell["source"])
+        if cell["cell_type"] == "code" and "def save_weights" in src and "def load_weights" in src:
+            exec(compile(src, "demo.ipynb:save_weights", "exec"), ns)
+            return ns["save_weights"], ns["load_weights"]
+    raise SystemExit("demo.ipynb: save_weights / load_weights not found")
+
+
+def gen_checkpoint(reference_path, ref):
+    """A tiny tied-head GPT saved by the reference's own ``save_weights``; logits of the reference on a small batch."""
+    network, layers, activations, ta = ref
+    spec = wl.GPTSpec("ckpt", vocab=40, context=16, d_model=32, heads=2, layers=2, tied_head=True, precision="tf32",
+                      batch=3, seq_len=12, input_seed=11, input_dist="uniform")
+    net = build_reference_net(ref, spec)
+    params = wl.seeded_params(spec, 77)
+    seen, it = set(), iter(params)
+    for layer in net.layers:
+        for prm in layer.parameters:
+            if id(prm) in seen:
+                continue
+            seen.add(id(prm))
+            prm[...] = next(it)
+    net.set_eval(True)
+    save_weights, _ = notebook_helpers(reference_path, ref)
+
+    class HostArray(np.ndarray):
+        # the notebook calls CuPy's .get() on every parameter; on the NumPy path the array is already on the host
+        def get(self):
+            return np.asarray(self)
+
+    class View:
+        def __init__(self, layer):
+            self.parameters = [prm.view(HostArray) for prm in layer.parameters]
+    View.__name__ = "View"
+
+    class Saved:
+        layers = []
+    for layer in net.layers:
+        v = type(type(layer).__name__, (View,), {})(layer)      # keeps type(layer).__name__ for the file's "name"
+        Saved.layers.append(v)
+    save_weights(Saved, os.path.join(HERE, "ckpt_tiny.pkl"))
+    ids = wl.make_inputs(spec)
+    logits = np.asarray(net.predict(ids), dtype=np.float32)
+    np.savez_compressed(os.path.join(HERE, "ckpt_tiny.npz"), ids=ids, logits=logits,
+                        spec=np.array([spec.vocab, spec.context, spec.d_model, spec.heads, spec.layers]))
+    print("ckpt_tiny: logits", logits.shape, "file", os.path.getsize(os.path.join(HERE, "ckpt_tiny.pkl")), "bytes")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -310,6 +364,8 @@ def main():
             gen_large(ref, "c5", 1)
         elif w == "c4":
             gen_decode(ref)
+        elif w == "ckpt":
+            gen_checkpoint(a.reference, ref)
         else:
             raise SystemExit(f"unknown target {w}")
 

@@ -462,12 +462,16 @@ int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H,
             return TLNN_OK;
         }
     }
+    if constexpr (HD < 32) {
+        TL_REQUIRE(false, "attention: head dimension %d in float32 mode needs 16-byte aligned buffers", HD);
+    } else {
     dim3 grid((T + F32_QPB - 1) / F32_QPB, B * H);
     if (causal)
         TL_LAUNCH(ctx, "attention_f32_causal", attention_f32_kernel<HD, true><<<grid, 128, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
     else
         TL_LAUNCH(ctx, "attention_f32_full", attention_f32_kernel<HD, false><<<grid, 128, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
     return TLNN_OK;
+    }
 }
 
 }  // namespace
@@ -504,9 +508,11 @@ int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int o
     const float* q = reinterpret_cast<const float*>(qkv);
     float* o = reinterpret_cast<float*>(out);
     const int round_out = out_kind == TL_OUT_TF32;
+    if (hd == 8) return launch_f32<8>(ctx, q, o, B, T, heads, causal, round_out);
+    if (hd == 16) return launch_f32<16>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 32) return launch_f32<32>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 64) return launch_f32<64>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 96) return launch_f32<96>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 128) return launch_f32<128>(ctx, q, o, B, T, heads, causal, round_out);
-    TL_REQUIRE(false, "attention: head dimension %d is not supported in float32 mode (32, 64, 96 or 128)", hd);
+    TL_REQUIRE(false, "attention: head dimension %d is not supported in float32 mode (8, 16, 32, 64, 96 or 128)", hd);
 }
