@@ -402,6 +402,18 @@ def run_other(args, spec):
         step = lambda: xp.argmax(net.predict(xd))
         units, metric, unit = spec.batch, "vit_forward_images_per_s", "images/s"
         flops = spec.flops_per_image() * spec.batch
+    elif args.sample:
+        # the notebook's generation loop (sampling from the model's SoftMax output), on the KV cache
+        from torchless_nn_b200.activations import SoftMax
+        from torchless_nn_b200.network import Network
+        rows = args.batch or spec.batch
+        x = x[:rows]
+        sampler = Network(net.layers + [SoftMax()])
+        sampler.set_eval(True)
+        uniforms = np.random.default_rng(7).random((args.new_tokens, rows))
+        step = lambda: sampler.generate(x, args.new_tokens, uniforms=uniforms)
+        units, metric, unit = rows * args.new_tokens, "gpt_sampled_decode_new_tokens_per_s", "tokens/s"
+        flops = None
     else:
         step = lambda: net.generate_greedy(x, args.new_tokens)
         units, metric, unit = spec.batch * args.new_tokens, "gpt_greedy_decode_new_tokens_per_s", "tokens/s"
@@ -425,14 +437,18 @@ def run_other(args, spec):
     line = {"metric": metric, "value": units * args.steps / (ms.value * 1e-3), "unit": unit, "n_gpus": 1, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms.value / args.steps, "higher_is_better": True,
             "dtype": "bf16" if spec.precision == "bf16" else "tf32", "data": "synthetic",
-            "config": {"workload": spec.name}, "gpu_launches": int(launches), "kernel_classes_ms_per_step": classes}
+            "config": {"workload": spec.name + (f" sampled, {args.batch or spec.batch} rows" if getattr(args, "sample", False) and spec.kind == "gpt" else "")},
+            "gpu_launches": int(launches), "kernel_classes_ms_per_step": classes}
+    if spec.kind == "gpt":
+        line["ms_per_token"] = ms.value / args.steps / args.new_tokens
     if flops:
         line["tflops"] = flops * args.steps / (ms.value * 1e-3) / 1e12
     if spec.kind == "gpt":
         # decode is weight- and cache-streaming bound: bytes = weights once per step + K/V read per step
         d, L = spec.d_model, spec.layers
         w_bytes = 2.0 * (spec.n_params() - spec.context * d)          # bf16, tied table doubles as the head
-        kv = sum(2.0 * spec.batch * L * (spec.seq_len + i) * d * 2 for i in range(args.new_tokens))
+        kv = sum(2.0 * (args.batch or spec.batch if getattr(args, "sample", False) else spec.batch) * L * (spec.seq_len + i) * d * 2
+                 for i in range(args.new_tokens))
         total = w_bytes * args.new_tokens + kv
         line["hbm_bytes_per_run"] = total
         line["hbm_gbs_achieved_incl_prefill_time"] = total * args.steps / (ms.value * 1e-3) / 1e9
@@ -448,6 +464,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c5", choices=["c5", "c3", "c1", "c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sample", action="store_true", help="c4 only: sampled decode (the notebook's GPT.generate) instead of arg-max")
+    ap.add_argument("--batch", type=int, default=0, help="c4 --sample only: number of prompt rows (default: the config's 64)")
     ap.add_argument("--new-tokens", type=int, default=wl.C4_NEW_TOKENS, help="c4 only: tokens generated per prompt")
     args = ap.parse_args()
     spec = wl.CONFIGS[args.config]

@@ -122,6 +122,13 @@ int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long long rows, 
 /* xp.argmax(logits, axis=-1) (network.py:135,158): first index of the row maximum, int32. */
 int tlnn_argmax_fwd(tlnn_ctx* ctx, const float* x, long long ldx, int32_t* out, long long rows, int cols);
 
+/* xp.random.choice(xp.arange(V), p=probs) (demo.ipynb:1530, GPT.generate) for given uniform numbers: row r draws the
+ * first index i with cumsum(probs[r])[i] / sum(probs[r]) > uniforms[r] (NumPy's inverse-CDF rule, prefix sums in
+ * double); probs (rows, V) float32 with row pitch ldp, uniforms (rows) double in [0, 1) on the device, out int32.
+ * The random numbers are the caller's: the library keeps no generator state. */
+int tlnn_sample_fwd(tlnn_ctx* ctx, const float* probs, long long ldp, const double* uniforms, int32_t* out,
+                    long long rows, int cols);
+
 /* MultiHeadAttention.forward (layers.py:281-307).  x, out: (B, T, d) float32.  wqkv_t (3d, d) and
  * wo_t (d, d) are prepared weights; causal != 0 applies the decoder mask of layers.py:254-256,295-296. */
 int tlnn_attention_fwd(tlnn_ctx* ctx, int prec, const float* x, const void* wqkv_t, const float* bqkv,
@@ -207,6 +214,13 @@ int tlnn_decode_step(tlnn_decoder* dec, const int32_t* prev_tokens, int32_t* nex
 /* Runs n_steps steps back to back; tokens_out is (B, n_steps) int32 row-major on the device, column 0
  * being the token that follows `prev_tokens`. */
 int tlnn_decode_run(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, int32_t* tokens_out);
+/* Sampling forms (demo.ipynb:1530, `random.choice(arange(V), p=probs)` after the model's SoftMax layer): the token of
+ * every row is drawn from softmax(logits / temperature) with the inverse-CDF rule of tlnn_sample_fwd.  `uniforms` is
+ * HOST memory: (B) for the first token, (n_steps, B) row-major for a run.  tlnn_decode_first_sampled replaces the
+ * arg-max first token of tlnn_decode_begin and must be called right after it. */
+int tlnn_decode_first_sampled(tlnn_decoder* dec, float temperature, const double* uniforms, int32_t* first_tokens);
+int tlnn_decode_run_sampled(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, float temperature,
+                            const double* uniforms, int32_t* tokens_out);
 int tlnn_decode_end(tlnn_decoder* dec);
 
 /* ---- profiling -------------------------------------------------------------- */

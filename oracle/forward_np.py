@@ -217,3 +217,35 @@ def tokens_match(got, ref_argmax, ref_top, ref_second, tol_abs):
     differ = got != ref_argmax
     excused = (ref_top - ref_second) < tol_abs
     return bool(np.all(~differ | excused)), int(differ.sum()), int((differ & ~excused).sum())
+
+
+def choice_index(probs, u):
+    """numpy.random.RandomState.choice(arange(V), p=probs) for a given uniform number u (the NumPy runtime of
+    demo.ipynb:1530): cdf = cumsum(p) in double, cdf /= cdf[-1], first index with cdf > u."""
+    cdf = np.cumsum(np.asarray(probs, dtype=np.float64))
+    cdf /= cdf[-1]
+    return int(min(np.searchsorted(cdf, u, side="right"), len(cdf) - 1))
+
+
+def sample_generate(forward_probs, seed_tokens, length, context, uniforms):
+    """demo.ipynb:1520-1535 (GPT.generate) for B rows: crop to the last ``context`` tokens, run the model
+    (``forward_probs(ids) -> (B, T, V)`` probabilities), draw the next token of every row from the last position.
+    Returns (tokens (B, T0 + length), margins (length, B)) where a margin is the distance of the uniform number to
+    the nearest boundary of the chosen cell of the cdf: draws with a tiny margin may legitimately differ between two
+    implementations whose probabilities differ in the last digits."""
+    tokens = np.asarray(seed_tokens).astype(np.int64)
+    B = tokens.shape[0]
+    margins = np.zeros((length, B))
+    for step in range(length):
+        window = tokens[:, max(0, tokens.shape[1] - context):]
+        probs = forward_probs(window)[:, -1]
+        nxt = np.zeros((B, 1), dtype=np.int64)
+        for b in range(B):
+            cdf = np.cumsum(probs[b].astype(np.float64))
+            cdf /= cdf[-1]
+            i = choice_index(probs[b], uniforms[step, b])
+            lo = cdf[i - 1] if i > 0 else 0.0
+            margins[step, b] = min(uniforms[step, b] - lo, cdf[i] - uniforms[step, b])
+            nxt[b, 0] = i
+        tokens = np.concatenate([tokens, nxt], axis=1)
+    return tokens, margins

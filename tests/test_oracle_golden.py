@@ -116,3 +116,17 @@ def test_workload_generators():
     assert [wl.shard_rows(10, r, 4) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
     with pytest.raises(ValueError):
         wl.shard_rows(8, 4, 4)
+
+
+def test_choice_rule_is_numpys():
+    """The sampling oracle restates numpy.random.RandomState.choice(arange(V), p=p) - what `xp.random.choice` is on the
+    reference's NumPy runtime (demo.ipynb:1530) - for a given uniform number: pinned against NumPy itself."""
+    from oracle import forward_np as onp
+    rng = np.random.default_rng(0)
+    for V in (5, 65, 1000):
+        p = rng.random(V) ** 3
+        p /= p.sum()
+        for seed in range(25):
+            u = np.random.RandomState(seed).random_sample()
+            want = np.random.RandomState(seed).choice(np.arange(V), p=p)
+            assert onp.choice_index(p, u) == want

@@ -69,6 +69,7 @@ PROTOTYPES = {
     "tlnn_activation_fwd": (C.c_int, [vp, C.c_int, vp, vp, C.c_size_t]),
     "tlnn_softmax_fwd": (C.c_int, [vp, vp, vp, ll, C.c_int, C.c_float]),
     "tlnn_argmax_fwd": (C.c_int, [vp, vp, ll, vp, ll, C.c_int]),
+    "tlnn_sample_fwd": (C.c_int, [vp, vp, ll, vp, vp, ll, C.c_int]),
     "tlnn_attention_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tlnn_ffn_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, C.c_int, vp, ll, C.c_int]),
     "tlnn_block_fwd": (C.c_int, [vp, C.c_int, vp, C.POINTER(BlockParams), C.c_int, vp, C.c_int, C.c_int, C.c_int,
@@ -82,6 +83,8 @@ PROTOTYPES = {
     "tlnn_decode_begin": (C.c_int, [vp, C.POINTER(GPTModel), vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, c_void_pp]),
     "tlnn_decode_step": (C.c_int, [vp, vp, vp]),
     "tlnn_decode_run": (C.c_int, [vp, vp, C.c_int, vp]),
+    "tlnn_decode_first_sampled": (C.c_int, [vp, C.c_float, vp, vp]),
+    "tlnn_decode_run_sampled": (C.c_int, [vp, vp, C.c_int, C.c_float, vp, vp]),
     "tlnn_decode_end": (C.c_int, [vp]),
     "tlnn_prof_begin": (C.c_int, [vp]),
     "tlnn_prof_end": (C.c_int, [vp, C.POINTER(C.c_float)]),

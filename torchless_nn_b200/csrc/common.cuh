@@ -130,6 +130,9 @@ int tl_convert(tlnn_ctx* ctx, const float* x, long long ldx, void* out, int out_
 int tl_embed(tlnn_ctx* ctx, const void* ids, int ids_type, const float* table, const float* pos, float* out,
              int B, int T, int d, int vocab);
 int tl_argmax_partials(tlnn_ctx* ctx, const float2* partials, int n_parts, int32_t* tokens, long long rows);
+// Inverse-CDF draw per row; `step` (device, may be null) selects the block of `rows` uniform numbers to use.
+int tl_sample(tlnn_ctx* ctx, const float* probs, long long ldp, const double* uniforms, const int* step, int32_t* out,
+              long long rows, int cols);
 
 // Epilogue description of the tensor-core GEMM: out = act(acc + bias) + residual, with optional row remapping
 // (used by the ViT projector to drop patch rows behind the class token) and optional per-tile arg-max.

@@ -210,6 +210,13 @@ struct tlnn_decoder {
     int n_parts = 0;
     cudaGraphExec_t step_graph = nullptr;        // one captured step, replayed by tlnn_decode_run
     long long launches_per_step = 0;
+    // sampling (allocated by the first sampled call): logits and probabilities (B, vocab), uniform numbers (max_len, B)
+    char* sample_mem = nullptr;
+    float *logits = nullptr, *probs = nullptr;
+    double* uniforms = nullptr;
+    cudaGraphExec_t sample_graph = nullptr;      // one captured sampling step for sample_temperature
+    float sample_temperature = 0.f;
+    long long sample_launches_per_step = 0;
 };
 
 namespace {
@@ -239,7 +246,7 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
 }
 
 // One token for every sequence: cur tokens at position *d_len -> next tokens; advances the device counters.
-int decode_one(tlnn_decoder* dec) {
+int decode_one(tlnn_decoder* dec, bool sample = false, float temperature = 1.f) {
     tlnn_ctx* ctx = dec->ctx;
     const tlnn_gpt_model& m = dec->m;
     const int B = dec->B, d = m.d, prec = m.prec, kind = okind(prec);
@@ -272,9 +279,18 @@ int decode_one(tlnn_decoder* dec) {
     }
     TL_TRY(tl_layernorm(ctx, x, m.lnf_gamma, m.lnf_beta, 1e-5f, dec->a, kind, B, d));
     tl_gemm_epilogue eh;
-    eh.bias = m.head_bias; eh.argmax_partials = dec->parts;
-    TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
-    TL_TRY(tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B));
+    eh.bias = m.head_bias;
+    if (sample) {
+        // logits -> softmax(logits / temperature) -> draw with this step's uniform numbers
+        eh.out = dec->logits; eh.ldo = m.vocab; eh.out_kind = TL_OUT_F32;
+        TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
+        TL_TRY(tlnn_softmax_fwd(ctx, dec->logits, dec->probs, B, m.vocab, temperature));
+        TL_TRY(tl_sample(ctx, dec->probs, m.vocab, dec->uniforms, dec->d_step, dec->next, B, m.vocab));
+    } else {
+        eh.argmax_partials = dec->parts;
+        TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
+        TL_TRY(tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B));
+    }
     TL_LAUNCH(ctx, "decode_advance", decode_advance_kernel<<<1, 256, 0, ctx->stream>>>(dec->next, dec->cur, dec->d_sink,
                                                                                       dec->d_len, dec->d_step, B));
     return TLNN_OK;
@@ -438,11 +454,92 @@ extern "C" int tlnn_decode_run(tlnn_decoder* dec, const int32_t* prev_tokens, in
     return TLNN_OK;
 }
 
+namespace {
+int ensure_sampling_buffers(tlnn_decoder* dec) {
+    if (dec->sample_mem) return TLNN_OK;
+    const size_t row = ((size_t)dec->B * dec->m.vocab * 4 + 255) & ~size_t(255);
+    const size_t un = ((size_t)dec->max_len * dec->B * 8 + 255) & ~size_t(255);
+    TL_CUDA(cudaMalloc(&dec->sample_mem, 2 * row + un));
+    dec->logits = (float*)dec->sample_mem;
+    dec->probs = (float*)(dec->sample_mem + row);
+    dec->uniforms = (double*)(dec->sample_mem + 2 * row);
+    return TLNN_OK;
+}
+}  // namespace
+
+extern "C" int tlnn_decode_first_sampled(tlnn_decoder* dec, float temperature, const double* uniforms, int32_t* first_tokens) {
+    TL_NOTNULL(dec); TL_NOTNULL(uniforms); TL_NOTNULL(first_tokens);
+    tlnn_ctx* ctx = dec->ctx;
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_REQUIRE(temperature > 0.f, "decode: the temperature must be positive");
+    TL_REQUIRE(dec->host_len < dec->max_len && dec->step_graph == nullptr && dec->sample_graph == nullptr,
+               "decode: the first token is drawn right after tlnn_decode_begin, before any step");
+    TL_TRY(ensure_sampling_buffers(dec));
+    const tlnn_gpt_model& m = dec->m;
+    // dec->a still holds the normalised last prompt rows of tlnn_decode_begin
+    TL_CUDA(cudaMemcpyAsync(dec->uniforms, uniforms, (size_t)dec->B * 8, cudaMemcpyHostToDevice, ctx->stream));
+    tl_gemm_epilogue eh;
+    eh.bias = m.head_bias; eh.out = dec->logits; eh.ldo = m.vocab; eh.out_kind = TL_OUT_F32;
+    TL_TRY(tl_gemm(ctx, m.prec, dec->a, m.d, m.head_t, m.d, dec->B, m.vocab, m.d, eh));
+    TL_TRY(tlnn_softmax_fwd(ctx, dec->logits, dec->probs, dec->B, m.vocab, temperature));
+    TL_TRY(tl_sample(ctx, dec->probs, m.vocab, dec->uniforms, nullptr, dec->next, dec->B, m.vocab));
+    TL_CUDA(cudaMemcpyAsync(dec->cur, dec->next, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_CUDA(cudaMemcpyAsync(first_tokens, dec->next, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_CUDA(cudaStreamSynchronize(ctx->stream));            // `uniforms` is the caller's host memory
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_decode_run_sampled(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, float temperature,
+                                       const double* uniforms, int32_t* tokens_out) {
+    TL_NOTNULL(dec); TL_NOTNULL(prev_tokens); TL_NOTNULL(tokens_out); TL_NOTNULL(uniforms);
+    tlnn_ctx* ctx = dec->ctx;
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_REQUIRE(temperature > 0.f, "decode: the temperature must be positive");
+    TL_REQUIRE(n_steps >= 0 && dec->host_len + n_steps <= dec->max_len, "decode: %d steps do not fit the cache (%d of %d used)",
+               n_steps, dec->host_len, dec->max_len);
+    if (n_steps == 0) return TLNN_OK;
+    TL_TRY(ensure_sampling_buffers(dec));
+    if (prev_tokens != dec->cur)
+        TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    TL_CUDA(cudaMemcpyAsync(dec->uniforms, uniforms, (size_t)n_steps * dec->B * 8, cudaMemcpyHostToDevice, ctx->stream));
+    TL_CUDA(cudaStreamSynchronize(ctx->stream));            // `uniforms` is the caller's host memory
+    TL_TRY(set_sink(dec, tokens_out, n_steps));
+    TL_CUDA(cudaMemsetAsync(dec->d_step, 0, sizeof(int), ctx->stream));
+    if (!ctx->prof_classes && (!dec->sample_graph || dec->sample_temperature != temperature)) {
+        if (dec->sample_graph) { cudaGraphExecDestroy(dec->sample_graph); dec->sample_graph = nullptr; }
+        cudaGraph_t graph = nullptr;
+        const long long before = ctx->launches;
+        TL_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const int st = decode_one(dec, true, temperature);
+        dec->sample_launches_per_step = ctx->launches - before;
+        ctx->launches = before;
+        const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+        if (st != TLNN_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (ce != cudaSuccess) return tl_cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
+        const cudaError_t ie = cudaGraphInstantiate(&dec->sample_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) { dec->sample_graph = nullptr; return tl_cuda_fail(ie, "cudaGraphInstantiate", __FILE__, __LINE__); }
+        dec->sample_temperature = temperature;
+    }
+    for (int s = 0; s < n_steps; s++) {
+        if (dec->sample_graph && !ctx->prof_classes) {
+            TL_CUDA(cudaGraphLaunch(dec->sample_graph, ctx->stream));
+            ctx->launches += dec->sample_launches_per_step;
+        } else {
+            TL_TRY(decode_one(dec, true, temperature));
+        }
+        dec->host_len++;
+    }
+    return TLNN_OK;
+}
+
 extern "C" int tlnn_decode_end(tlnn_decoder* dec) {
     if (!dec) return TLNN_OK;
     cudaSetDevice(dec->ctx->device);
     cudaStreamSynchronize(dec->ctx->stream);
     if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
+    if (dec->sample_graph) cudaGraphExecDestroy(dec->sample_graph);
+    if (dec->sample_mem) cudaFree(dec->sample_mem);
     cudaFree(dec->mem);
     delete dec;
     return TLNN_OK;

@@ -483,6 +483,59 @@ extern "C" int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long 
     return TLNN_OK;
 }
 
+namespace {
+// Inverse-CDF draw, one block per row.  Thread t owns the contiguous segment t of the row: segment sums (double),
+// an exclusive scan of the 256 sums, then the thread whose segment holds the target walks it.  The comparison is
+// NumPy's: prefix / total > u.
+// The uniform number of row r is uniforms[step * rows + r], with the step read from device memory when given (a
+// decode step captured in a CUDA graph advances it on the device).
+__global__ void __launch_bounds__(256) sample_kernel(const float* __restrict__ probs, long long ldp, const double* __restrict__ uniforms,
+                                                     const int* __restrict__ step, int32_t* __restrict__ out, int cols) {
+    __shared__ double seg[256];
+    __shared__ int found;
+    const long long row = blockIdx.x;
+    const float* p = probs + row * ldp;
+    const int per = (cols + 255) / 256;
+    const int lo = min(cols, (int)threadIdx.x * per), hi = min(cols, lo + per);
+    double s = 0.0;
+    for (int i = lo; i < hi; i++) s += (double)p[i];
+    seg[threadIdx.x] = s;
+    if (threadIdx.x == 0) found = cols - 1;          // u so close to 1 that no prefix exceeds it: the last index
+    __syncthreads();
+    double before = 0.0, total = 0.0;
+    for (int t = 0; t < 256; t++) {
+        if (t == (int)threadIdx.x) before = total;
+        total += seg[t];
+    }
+    const double u = uniforms[(step ? (long long)*step * gridDim.x : 0ll) + row];
+    double c = before;
+    int mine = cols;
+    for (int i = lo; i < hi; i++) {
+        c += (double)p[i];
+        if (c / total > u) { mine = i; break; }
+    }
+    if (mine < cols) atomicMin(&found, mine);
+    __syncthreads();
+    if (threadIdx.x == 0) out[row] = found;
+}
+}  // namespace
+
+int tl_sample(tlnn_ctx* ctx, const float* probs, long long ldp, const double* uniforms, const int* step, int32_t* out,
+              long long rows, int cols) {
+    TL_LAUNCH(ctx, "sample", sample_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(probs, ldp, uniforms, step, out, cols));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_sample_fwd(tlnn_ctx* ctx, const float* probs, long long ldp, const double* uniforms, int32_t* out,
+                               long long rows, int cols) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31) && ldp >= cols, "sample: bad shape rows=%lld cols=%d", rows, cols);
+    if (rows == 0) return TLNN_OK;
+    TL_NOTNULL(probs); TL_NOTNULL(uniforms); TL_NOTNULL(out);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    return tl_sample(ctx, probs, ldp, uniforms, nullptr, out, rows, cols);
+}
+
 extern "C" int tlnn_argmax_fwd(tlnn_ctx* ctx, const float* x, long long ldx, int32_t* out, long long rows, int cols) {
     TL_NOTNULL(ctx);
     TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31) && ldx >= cols, "argmax: bad shape rows=%lld cols=%d", rows, cols);

@@ -128,6 +128,89 @@ class Network:
             return tokens
         return argmax_last(self.predict(input))
 
+    def generate(self, seed_tokens, length: int, uniforms=None, seed=None, use_cache: bool = True):
+        """The notebook's ``GPT.generate`` (demo.ipynb:1520-1535) for every row of ``seed_tokens``: each step crops
+        the tokens to the last ``context_length`` (the sliding window of demo.ipynb:1528, positions restart at the
+        crop), runs the model, takes the probabilities of the last position and draws the next token as
+        ``random.choice(arange(V), p=probs)`` does on the NumPy runtime: the first index whose normalised prefix sum
+        exceeds a uniform number.  ``uniforms`` (length, B) supplies those numbers; by default they come from
+        ``numpy.random.default_rng(seed)``.  The model's output must be probabilities (a trailing ``SoftMax``), as in
+        the notebook; a model that ends in logits gets ``SoftMax()`` applied.  Returns (B, T0 + length) int32 on the
+        host.
+
+        Steps that need no crop run on the per-layer KV cache (``tlnn_decode_run_sampled``; ``use_cache=False`` forces
+        the window path); once the window slides, positions restart at the crop, the cache no longer applies and every
+        step re-runs the window like the reference, with only the last position going through the row-wise tail of the
+        model (final LayerNorm, head, SoftMax): B x V probabilities per step instead of B x T x V."""
+        from .activations import SoftMax
+        self._check_eval()
+        tokens = np.asarray(as_token_ids(seed_tokens).get()).astype(np.int32)
+        if tokens.ndim != 2 or tokens.shape[1] < 1:
+            raise ValueError("generate needs a (B, T0 >= 1) array of token ids")
+        B = tokens.shape[0]
+        front = self.layers[0]
+        if not isinstance(front, GPTEmbedFront):
+            raise ValueError("generate needs a model that starts with GPTEmbedFront")
+        context = front.context_length
+        if uniforms is None:
+            uniforms = np.random.default_rng(seed).random((length, B))
+        uniforms = np.ascontiguousarray(np.asarray(uniforms, dtype=np.float64).reshape(length, B))
+        # the row-wise tail starts after the last attention block
+        split = max(i for i, l in enumerate(self.layers) if isinstance(l, TransformerBlock)) + 1 \
+            if any(isinstance(l, TransformerBlock) for l in self.layers) else 1
+        body, tail = self.layers[:split], self.layers[split:]
+        ends_in_probs = bool(tail) and isinstance(tail[-1], SoftMax)
+        extra = None if ends_in_probs else SoftMax()
+        u_dev = DeviceArray((B * 8,), np.uint8)          # B doubles (the device array type has no float64)
+        picked = DeviceArray((B,), np.int32)
+        first_step = 0
+        # While prompt + continuation fit the context nothing is cropped, so the per-layer KV cache gives the same
+        # tokens without re-running the window: those steps go through the decoder (one CUDA graph replay each).
+        core = self.layers[:-1] if ends_in_probs else self.layers
+        plan = GPTPlan.match(core) if use_cache else None
+        cached = min(length, context - tokens.shape[1]) if plan is not None else 0
+        if plan is not None and plan.blocks:
+            ab = plan.blocks[0].attn_block
+            if ab.embedding_dim // ab.num_heads not in (32, 64, 128):      # head sizes of the decode attention kernel
+                cached = 0
+        if cached >= 1:
+            temperature = float(tail[-1].temperature) if ends_in_probs else 1.0
+            m, keep, V = plan.model()
+            ids = as_token_ids(tokens)
+            T0 = tokens.shape[1]
+            first = DeviceArray((B,), np.int32)
+            dec = C.c_void_p()
+            check(lib.tlnn_decode_begin(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T0, T0 + cached,
+                                        first.ptr, C.byref(dec)))
+            try:
+                check(lib.tlnn_decode_first_sampled(dec, temperature, uniforms[0].ctypes.data, first.ptr))
+                new = [first.get().reshape(B, 1)]
+                if cached > 1:
+                    rest = DeviceArray((B, cached - 1), np.int32)
+                    check(lib.tlnn_decode_run_sampled(dec, first.ptr, cached - 1, temperature,
+                                                      uniforms[1:cached].ctypes.data, rest.ptr))
+                    new.append(rest.get())
+            finally:
+                lib.tlnn_decode_end(dec)
+            tokens = np.concatenate([tokens] + [n.astype(np.int32) for n in new], axis=1)
+            first_step = cached
+        for step in range(first_step, length):
+            window = tokens[:, max(0, tokens.shape[1] - context):]
+            x = as_token_ids(window)
+            for layer in body:
+                x = layer.forward(x)
+            T, d = x.shape[1], x.shape[2]
+            last = x[:, T - 1:T, :] if T > 1 else x
+            for layer in tail:
+                last = layer.forward(last)
+            if extra is not None:
+                last = extra.forward(last)
+            V = last.shape[-1]
+            check(lib.tlnn_h2d(backend.ctx(), u_dev.ptr, uniforms[step].ctypes.data, uniforms[step].nbytes))
+            check(lib.tlnn_sample_fwd(backend.ctx(), last.ptr, V, u_dev.ptr, picked.ptr, B, V))
+            tokens = np.concatenate([tokens, picked.get().reshape(B, 1).astype(np.int32)], axis=1)
+        return tokens
+
     def generate_greedy(self, prompts, new_tokens: int):
         """Greedy continuation of every prompt row by ``new_tokens`` tokens; returns (B, T0 + new_tokens) int32 on
         the device.  Prompt plus continuation must fit the context length (the notebook's sliding window beyond it,
