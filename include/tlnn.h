@@ -122,6 +122,14 @@ int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long long rows, 
 /* xp.argmax(logits, axis=-1) (network.py:135,158): first index of the row maximum, int32. */
 int tlnn_argmax_fwd(tlnn_ctx* ctx, const float* x, long long ldx, int32_t* out, long long rows, int cols);
 
+/* One batch of Network.evaluate (network.py:145-160) on the device: for every row of probs (rows, V, pitch ldp)
+ * adds -log(probs[row, label] + 1e-7) (CrossEntropy.loss, network.py:19-22) to *loss_sum and 1 to *correct when the
+ * first index of the row maximum equals the label (xp.argmax, network.py:158).  Both accumulators live on the device
+ * (double and 64-bit integer) and are not cleared by the call; labels are TLNN_I32, TLNN_I64 or TLNN_U8.  A label
+ * outside [0, V) is reported as TLNN_ERR_INDEX at the next sync, as NumPy's indexing would raise. */
+int tlnn_eval_batch_fwd(tlnn_ctx* ctx, const float* probs, long long ldp, const void* labels, int labels_type,
+                        long long rows, int cols, double* loss_sum, long long* correct);
+
 /* xp.random.choice(xp.arange(V), p=probs) (demo.ipynb:1530, GPT.generate) for given uniform numbers: row r draws the
  * first index i with cumsum(probs[r])[i] / sum(probs[r]) > uniforms[r] (NumPy's inverse-CDF rule, prefix sums in
  * double); probs (rows, V) float32 with row pitch ldp, uniforms (rows) double in [0, 1) on the device, out int32.
@@ -222,6 +230,23 @@ int tlnn_decode_first_sampled(tlnn_decoder* dec, float temperature, const double
 int tlnn_decode_run_sampled(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, float temperature,
                             const double* uniforms, int32_t* tokens_out);
 int tlnn_decode_end(tlnn_decoder* dec);
+
+/* ---- double-buffered host feed ------------------------------------------- */
+/* The reference uploads every batch synchronously (`xp.array(batch)`, network.py:117,152).  A feeder owns two pinned
+ * host buffers, two device buffers and a copy stream: while the compute stream works on the batch in one slot, the
+ * next batch is written into the other slot's host buffer and copied.  Per batch: write into tlnn_feed_host(slot),
+ * tlnn_feed_submit(slot, bytes) (asynchronous copy; waits, on the copy stream, until the compute stream has released
+ * the slot's device buffer), later tlnn_feed_acquire(slot, &dev) (the compute stream waits for the copy), enqueue the
+ * work that reads dev, tlnn_feed_release(slot).  Before rewriting a slot's HOST buffer call tlnn_feed_host_wait(slot),
+ * which blocks the calling thread until that slot's last copy has left the buffer. */
+typedef struct tlnn_feeder tlnn_feeder;
+int tlnn_feed_create(tlnn_ctx* ctx, size_t bytes_per_batch, tlnn_feeder** out);
+int tlnn_feed_host(tlnn_feeder* f, int slot, void** host);
+int tlnn_feed_host_wait(tlnn_feeder* f, int slot);
+int tlnn_feed_submit(tlnn_feeder* f, int slot, size_t bytes);
+int tlnn_feed_acquire(tlnn_feeder* f, int slot, void** dev);
+int tlnn_feed_release(tlnn_feeder* f, int slot);
+int tlnn_feed_destroy(tlnn_feeder* f);
 
 /* ---- profiling -------------------------------------------------------------- */
 /* CUDA-event timing of everything enqueued between begin and end on the compute stream (milliseconds). */

@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by running the UNMODIFIED
 reference library (luke-skynet/torchless-nn) on its NumPy path.
 
-    XP_RUNTIME=CPU python tests/golden/make_golden.py --reference /path/to/torchless-nn [c1 c2 layers c3 c4 c5 ckpt]
+    XP_RUNTIME=CPU python tests/golden/make_golden.py --reference /path/to/torchless-nn [c1 c2 layers c3 c4 c5 ckpt eval]
 
 The reference checkout is only needed to (re)generate fixtures; tests read the
 committed ``.npz`` files.  For each configuration the script builds the
@@ -347,6 +347,39 @@ def gen_checkpoint(reference_path, ref):
     print("ckpt_tiny: logits", logits.shape, "file", os.path.getsize(os.path.join(HERE, "ckpt_tiny.pkl")), "bytes")
 
 
+def gen_evaluate(ref):
+    """The demo's ViT recipe in small (demo.ipynb: VitProjector with register tokens, SiLU blocks with dropout rates,
+    LayerNorm, VitMLPHead, SiLU, Dropout, Dense, SoftMax) through the reference's own ``Network.evaluate``."""
+    network, layers, activations, ta = ref
+    E, H = 64, 2
+    net = network.Network(
+        [ta.VitProjector((3, 16, 16), (2, 2), E, num_registers=2)]
+        + [layers.TransformerBlock(E, 0, H, activations.SiLU, attn_dropout_rate=0.1, res_dropout_rate=0.1) for _ in range(2)]
+        + [layers.LayerNorm(E), ta.VitMLPHead(E, 32), activations.SiLU(), layers.Dropout(0.1), layers.Dense(32, 10),
+           activations.SoftMax()])
+    rng = np.random.default_rng(123)
+    params, seen = [], set()
+    for layer in net.layers:
+        for prm in layer.parameters:
+            if id(prm) in seen:
+                continue
+            seen.add(id(prm))
+            if prm.ndim == 1 and prm.shape[0] in (E, 4 * E, 3 * E, 32, 10):
+                new = rng.standard_normal(prm.shape) * 0.1 + (1.0 if np.all(np.asarray(prm) == 1) else 0.0)
+            else:
+                new = rng.standard_normal(prm.shape) / np.sqrt(prm.shape[0] if prm.ndim > 1 else 1.0) * 0.7
+            prm[...] = new.astype(np.float32)
+            params.append(np.array(prm, dtype=np.float32))
+    images = rng.standard_normal((20, 3, 16, 16)).astype(np.float32)
+    labels = rng.integers(0, 10, size=20).astype(np.int64)
+    loss, acc = net.evaluate(images, labels, network.CrossEntropy(10), batch_size=8)
+    probs = np.asarray(net.predict(images), dtype=np.float32)
+    out = {f"p{i}": a for i, a in enumerate(params)}
+    np.savez_compressed(os.path.join(HERE, "eval_tiny.npz"), images=images, labels=labels, loss=np.float64(loss),
+                        accuracy=np.float64(acc), probs=probs, n_params=np.int64(len(params)), **out)
+    print("eval_tiny: loss", float(loss), "accuracy", float(acc), "params", len(params))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -366,6 +399,8 @@ def main():
             gen_decode(ref)
         elif w == "ckpt":
             gen_checkpoint(a.reference, ref)
+        elif w == "eval":
+            gen_evaluate(ref)
         else:
             raise SystemExit(f"unknown target {w}")
 

@@ -70,6 +70,14 @@ PROTOTYPES = {
     "tlnn_softmax_fwd": (C.c_int, [vp, vp, vp, ll, C.c_int, C.c_float]),
     "tlnn_argmax_fwd": (C.c_int, [vp, vp, ll, vp, ll, C.c_int]),
     "tlnn_sample_fwd": (C.c_int, [vp, vp, ll, vp, vp, ll, C.c_int]),
+    "tlnn_feed_create": (C.c_int, [vp, C.c_size_t, C.POINTER(vp)]),
+    "tlnn_feed_host": (C.c_int, [vp, C.c_int, C.POINTER(vp)]),
+    "tlnn_feed_host_wait": (C.c_int, [vp, C.c_int]),
+    "tlnn_feed_submit": (C.c_int, [vp, C.c_int, C.c_size_t]),
+    "tlnn_feed_acquire": (C.c_int, [vp, C.c_int, C.POINTER(vp)]),
+    "tlnn_feed_release": (C.c_int, [vp, C.c_int]),
+    "tlnn_feed_destroy": (C.c_int, [vp]),
+    "tlnn_eval_batch_fwd": (C.c_int, [vp, vp, ll, vp, C.c_int, ll, C.c_int, vp, vp]),
     "tlnn_attention_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tlnn_ffn_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, C.c_int, vp, ll, C.c_int]),
     "tlnn_block_fwd": (C.c_int, [vp, C.c_int, vp, C.POINTER(BlockParams), C.c_int, vp, C.c_int, C.c_int, C.c_int,

@@ -162,6 +162,103 @@ extern "C" int tlnn_h2d(tlnn_ctx* ctx, void* dst, const void* src, size_t bytes)
     return TLNN_OK;
 }
 
+// ---- double-buffered host feed ------------------------------------------------------------------------------------
+struct tlnn_feeder {
+    tlnn_ctx* ctx = nullptr;
+    size_t bytes = 0;
+    cudaStream_t copy = nullptr;
+    void* host[2] = {nullptr, nullptr};
+    void* dev[2] = {nullptr, nullptr};
+    cudaEvent_t copied[2] = {nullptr, nullptr};      // recorded on the copy stream after a slot's copy
+    cudaEvent_t released[2] = {nullptr, nullptr};    // recorded on the compute stream when a slot's consumer is enqueued
+    bool has_copy[2] = {false, false}, has_release[2] = {false, false};
+};
+
+extern "C" int tlnn_feed_create(tlnn_ctx* ctx, size_t bytes_per_batch, tlnn_feeder** out) {
+    TL_NOTNULL(ctx); TL_NOTNULL(out);
+    TL_REQUIRE(bytes_per_batch > 0, "feed: a batch needs at least one byte");
+    TL_CUDA(cudaSetDevice(ctx->device));
+    tlnn_feeder* f = new tlnn_feeder();
+    f->ctx = ctx;
+    f->bytes = bytes_per_batch;
+    cudaError_t e = cudaStreamCreateWithFlags(&f->copy, cudaStreamNonBlocking);
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        e = cudaMallocHost(&f->host[i], bytes_per_batch);
+        if (e == cudaSuccess) e = cudaMalloc(&f->dev[i], bytes_per_batch);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&f->copied[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&f->released[i], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) {
+        tlnn_feed_destroy(f);
+        return tl_cuda_fail(e, "feed_create", __FILE__, __LINE__);
+    }
+    *out = f;
+    return TLNN_OK;
+}
+
+static int feed_slot_ok(tlnn_feeder* f, int slot) {
+    TL_NOTNULL(f);
+    TL_REQUIRE(slot == 0 || slot == 1, "feed: slot %d (0 or 1)", slot);
+    TL_CUDA(cudaSetDevice(f->ctx->device));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_host(tlnn_feeder* f, int slot, void** host) {
+    TL_TRY(feed_slot_ok(f, slot));
+    TL_NOTNULL(host);
+    *host = f->host[slot];
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_host_wait(tlnn_feeder* f, int slot) {
+    TL_TRY(feed_slot_ok(f, slot));
+    if (f->has_copy[slot]) TL_CUDA(cudaEventSynchronize(f->copied[slot]));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_submit(tlnn_feeder* f, int slot, size_t bytes) {
+    TL_TRY(feed_slot_ok(f, slot));
+    TL_REQUIRE(bytes <= f->bytes, "feed: %zu bytes submitted, the feeder holds %zu per batch", bytes, f->bytes);
+    // the device buffer may still be read by the work that consumed the previous batch of this slot
+    if (f->has_release[slot]) TL_CUDA(cudaStreamWaitEvent(f->copy, f->released[slot], 0));
+    if (bytes) TL_CUDA(cudaMemcpyAsync(f->dev[slot], f->host[slot], bytes, cudaMemcpyHostToDevice, f->copy));
+    TL_CUDA(cudaEventRecord(f->copied[slot], f->copy));
+    f->has_copy[slot] = true;
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_acquire(tlnn_feeder* f, int slot, void** dev) {
+    TL_TRY(feed_slot_ok(f, slot));
+    TL_NOTNULL(dev);
+    TL_REQUIRE(f->has_copy[slot], "feed: slot %d was acquired before anything was submitted to it", slot);
+    TL_CUDA(cudaStreamWaitEvent(f->ctx->stream, f->copied[slot], 0));
+    *dev = f->dev[slot];
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_release(tlnn_feeder* f, int slot) {
+    TL_TRY(feed_slot_ok(f, slot));
+    TL_CUDA(cudaEventRecord(f->released[slot], f->ctx->stream));
+    f->has_release[slot] = true;
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_feed_destroy(tlnn_feeder* f) {
+    if (!f) return TLNN_OK;
+    cudaSetDevice(f->ctx->device);
+    if (f->copy) cudaStreamSynchronize(f->copy);
+    cudaStreamSynchronize(f->ctx->stream);
+    for (int i = 0; i < 2; i++) {
+        if (f->host[i]) cudaFreeHost(f->host[i]);
+        if (f->dev[i]) cudaFree(f->dev[i]);
+        if (f->copied[i]) cudaEventDestroy(f->copied[i]);
+        if (f->released[i]) cudaEventDestroy(f->released[i]);
+    }
+    if (f->copy) cudaStreamDestroy(f->copy);
+    delete f;
+    return TLNN_OK;
+}
+
 extern "C" int tlnn_d2h_async(tlnn_ctx* ctx, void* dst, const void* src, size_t bytes) {
     TL_NOTNULL(ctx);
     if (bytes == 0) return TLNN_OK;

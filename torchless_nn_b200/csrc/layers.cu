@@ -9,25 +9,42 @@ inline int op_kind(int prec) { return prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_
 inline size_t op_size(int prec) { return prec == TLNN_PREC_BF16 ? 2 : 4; }
 inline bool prec_ok(int prec) { return prec == TLNN_PREC_BF16 || prec == TLNN_PREC_TF32; }
 
+// Token rows have a pitch of ldt >= p0 * p1 * C elements; the columns past the patch features are written as zeros
+// (the GEMM operand rows must be a multiple of 16 bytes).
 __global__ void patchify_kernel(const float* __restrict__ img, void* __restrict__ tokens, int out_kind, int B, int C,
-                                int H, int W, int p0, int p1) {
+                                int H, int W, int p0, int p1, int ldt) {
     const int nph = H / p0, npw = W / p1;
     const int tdim = p0 * p1 * C;
-    const long long total = (long long)B * nph * npw * tdim;
+    const long long total = (long long)B * nph * npw * ldt;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int f = (int)(i % tdim);
-        long long tok = i / tdim;
+        int f = (int)(i % ldt);
+        long long tok = i / ldt;
         int c = f % C, j = (f / C) % p1, ii = f / (C * p1);
         int pc = (int)(tok % npw), pr = (int)((tok / npw) % nph);
         long long b = tok / ((long long)npw * nph);
-        float v = img[((b * C + c) * H + (pr * p0 + ii)) * W + (pc * p1 + j)];
+        float v = f < tdim ? img[((b * C + c) * H + (pr * p0 + ii)) * W + (pc * p1 + j)] : 0.f;
         if (out_kind == TL_OUT_BF16) {
             reinterpret_cast<__nv_bfloat16*>(tokens)[i] = __float2bfloat16_rn(v);
         } else {
             uint32_t u = __float_as_uint(v);
             if ((u & 0x7f800000u) != 0x7f800000u) { u += 0x00000fffu + ((u >> 13) & 1u); u &= 0xffffe000u; }
             reinterpret_cast<float*>(tokens)[i] = __uint_as_float(u);
+        }
+    }
+}
+
+// dst (rows, ldd) <- src (rows, cols) with zero columns appended; elements of `esz` bytes (2 or 4)
+__global__ void pad_rows_kernel(const void* __restrict__ src, void* __restrict__ dst, int rows, int cols, int ldd, int esz) {
+    const long long total = (long long)rows * ldd;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = (int)(i % ldd);
+        const long long r = i / ldd;
+        if (esz == 2) {
+            reinterpret_cast<uint16_t*>(dst)[i] = c < cols ? reinterpret_cast<const uint16_t*>(src)[r * cols + c] : (uint16_t)0;
+        } else {
+            reinterpret_cast<uint32_t*>(dst)[i] = c < cols ? reinterpret_cast<const uint32_t*>(src)[r * cols + c] : 0u;
         }
     }
 }
@@ -264,25 +281,37 @@ extern "C" int tlnn_vit_project_fwd(tlnn_ctx* ctx, int prec, const float* img, c
     TL_REQUIRE(B >= 0 && C > 0 && H > 0 && W > 0 && ph > 0 && pw > 0 && d > 0 && regs >= 0, "vit_project: bad shape");
     TL_REQUIRE(H % ph == 0 && W % pw == 0, "vit_project: image %dx%d is not a multiple of the patch %dx%d", H, W, ph, pw);
     const int tdim = ph * pw * C, n_patch = (H / ph) * (W / pw), n_cls = 1 + regs, T = n_cls + n_patch;
-    TL_REQUIRE(tdim % 8 == 0, "vit_project: the patch feature width %d must be a multiple of 8", tdim);
     if (B == 0) return TLNN_OK;
     TL_NOTNULL(img);
     TL_CUDA(cudaSetDevice(ctx->device));
     const long long M = (long long)B * n_patch;
-    TL_TRY(tl_ws_reserve(ctx, tl_ws_round((size_t)M * tdim * op_size(prec))));
+    // A patch feature width that is not a multiple of 8 (the demo's 2 x 2 x 3 = 12) is padded with zero columns on
+    // both operands: the GEMM wants operand rows of a multiple of 16 bytes.
+    const int ldt = (tdim + 7) / 8 * 8;
+    const bool padded = ldt != tdim;
+    TL_TRY(tl_ws_reserve(ctx, tl_ws_round((size_t)M * ldt * op_size(prec)) + tl_ws_round((size_t)d * ldt * op_size(prec))));
     tl_ws_cursor cur(ctx);
-    void* tok = cur.take<char>((size_t)M * tdim * op_size(prec));
-    {
-        size_t n = (size_t)M * tdim;
+    void* tok = cur.take<char>((size_t)M * ldt * op_size(prec));
+    const void* weight = proj_t;
+    if (padded) {
+        void* wp = cur.take<char>((size_t)d * ldt * op_size(prec));
+        size_t n = (size_t)d * ldt;
         int grid = (int)((n + 255) / 256);
         if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
-        TL_LAUNCH(ctx, "vit_patchify", patchify_kernel<<<grid, 256, 0, ctx->stream>>>(img, tok, op_kind(prec), B, C, H, W, ph, pw));
+        TL_LAUNCH(ctx, "vit_pad_weight", pad_rows_kernel<<<grid, 256, 0, ctx->stream>>>(proj_t, wp, d, tdim, ldt, (int)op_size(prec)));
+        weight = wp;
+    }
+    {
+        size_t n = (size_t)M * ldt;
+        int grid = (int)((n + 255) / 256);
+        if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
+        TL_LAUNCH(ctx, "vit_patchify", patchify_kernel<<<grid, 256, 0, ctx->stream>>>(img, tok, op_kind(prec), B, C, H, W, ph, pw, ldt));
     }
     tl_gemm_epilogue e;
     e.residual = pos; e.ldr = d; e.res_row_mod = n_patch; e.res_row_off = n_cls;     // + positional row of the patch
     e.out = out; e.ldo = d; e.out_kind = TL_OUT_F32;
     e.row_group = n_patch; e.out_group = T; e.out_off = n_cls;                        // patch rows sit behind the class rows
-    TL_TRY(tl_gemm(ctx, prec, tok, tdim, proj_t, tdim, (int)M, d, tdim, e));
+    TL_TRY(tl_gemm(ctx, prec, tok, ldt, weight, ldt, (int)M, d, ldt, e));
     {
         size_t n = (size_t)B * n_cls * d;
         int grid = (int)((n + 255) / 256);

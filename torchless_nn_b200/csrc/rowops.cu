@@ -536,6 +536,64 @@ extern "C" int tlnn_sample_fwd(tlnn_ctx* ctx, const float* probs, long long ldp,
     return tl_sample(ctx, probs, ldp, uniforms, nullptr, out, rows, cols);
 }
 
+namespace {
+__device__ __forceinline__ long long label_at(const void* labels, int type, long long i) {
+    if (type == TLNN_I32) return reinterpret_cast<const int32_t*>(labels)[i];
+    if (type == TLNN_I64) return reinterpret_cast<const long long*>(labels)[i];
+    return reinterpret_cast<const uint8_t*>(labels)[i];
+}
+
+// One block per row: first index of the row maximum against the label, and the row's cross-entropy term.
+__global__ void __launch_bounds__(256) eval_batch_kernel(const float* __restrict__ probs, long long ldp, const void* __restrict__ labels,
+                                                         int labels_type, int cols, double* loss_sum, unsigned long long* correct,
+                                                         tlnn_dev_err* err) {
+    __shared__ float best_v[256];
+    __shared__ int best_i[256];
+    const long long row = blockIdx.x;
+    const float* p = probs + row * ldp;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = p[i];
+        if (v > bv) { bv = v; bi = i; }           // strided scan keeps the smallest index of a thread's maximum
+    }
+    best_v[threadIdx.x] = bv; best_i[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) {
+            const float ov = best_v[threadIdx.x + s];
+            const int oi = best_i[threadIdx.x + s];
+            if (ov > best_v[threadIdx.x] || (ov == best_v[threadIdx.x] && oi < best_i[threadIdx.x])) {
+                best_v[threadIdx.x] = ov; best_i[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const long long label = label_at(labels, labels_type, row);
+        if (label < 0 || label >= cols) {
+            tl_dev_fail(err, TLNN_ERR_INDEX, 301, label);
+            return;
+        }
+        atomicAdd(loss_sum, (double)(-logf(p[label] + 1e-7f)));
+        if (best_i[0] == (int)label) atomicAdd(correct, 1ull);
+    }
+}
+}  // namespace
+
+extern "C" int tlnn_eval_batch_fwd(tlnn_ctx* ctx, const float* probs, long long ldp, const void* labels, int labels_type,
+                                   long long rows, int cols, double* loss_sum, long long* correct) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31) && ldp >= cols, "eval: bad shape rows=%lld cols=%d", rows, cols);
+    TL_REQUIRE(labels_type == TLNN_I32 || labels_type == TLNN_I64 || labels_type == TLNN_U8, "eval: labels must be int32, int64 or uint8");
+    if (rows == 0) return TLNN_OK;
+    TL_NOTNULL(probs); TL_NOTNULL(labels); TL_NOTNULL(loss_sum); TL_NOTNULL(correct);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "eval_batch", eval_batch_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(
+                  probs, ldp, labels, labels_type, cols, loss_sum, reinterpret_cast<unsigned long long*>(correct), ctx->d_err));
+    return TLNN_OK;
+}
+
 extern "C" int tlnn_argmax_fwd(tlnn_ctx* ctx, const float* x, long long ldx, int32_t* out, long long rows, int cols) {
     TL_NOTNULL(ctx);
     TL_REQUIRE(rows >= 0 && cols > 0 && rows < (1ll << 31) && ldx >= cols, "argmax: bad shape rows=%lld cols=%d", rows, cols);

@@ -71,6 +71,30 @@ class GPTPlan:
         return m, arr, V
 
 
+class CrossEntropy:
+    """The criterion ``Network.evaluate`` takes (network.py:11-25).  Only ``loss`` has a meaning on the forward path:
+    ``-sum(log(probs[label] + 1e-7))`` over a batch of probabilities; ``gradients`` belongs to training."""
+
+    def __init__(self, num_classes):
+        self.num_classes = int(num_classes)
+
+    def gradients(self, logits, labels):
+        raise NotImplementedError("the B200 runtime implements the forward path only")
+
+    def loss(self, probs, labels):
+        probs = as_device(probs, np.float32)
+        V = probs.shape[-1]
+        rows = probs.size // V
+        y = as_token_ids(np.asarray(labels.get() if isinstance(labels, DeviceArray) else labels).reshape(rows))
+        acc = DeviceArray((16,), np.uint8)
+        check(lib.tlnn_memset(backend.ctx(), acc.ptr, 0, 16))
+        check(lib.tlnn_eval_batch_fwd(backend.ctx(), probs.ptr, V, y.ptr, _ids_code(y), rows, V, acc.ptr, acc.ptr + 8))
+        return float(acc.get()[:8].view(np.float64)[0])
+
+    def num_samples(self, labels):
+        return int(np.prod(np.shape(labels)))
+
+
 class Network:
 
     def __init__(self, layers: list):
@@ -127,6 +151,28 @@ class Network:
             check(lib.tlnn_gpt_prefill(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T, None, tokens.ptr))
             return tokens
         return argmax_last(self.predict(input))
+
+    def evaluate(self, test_data, test_labels, criterion=None, batch_size=64):
+        """network.py:145-160: mean cross-entropy and accuracy of ``predict`` over ``test_data`` in batches.  The
+        arg-max, its comparison with the labels and the loss terms stay on the device; two numbers come back at the
+        end.  ``criterion`` is accepted for signature compatibility (its ``loss`` is what is computed)."""
+        self.set_eval(True)
+        n = len(test_data)
+        labels = np.asarray(test_labels)
+        acc = DeviceArray((16,), np.uint8)
+        check(lib.tlnn_memset(backend.ctx(), acc.ptr, 0, 16))
+        for i in range(0, n, batch_size):
+            hi = min(i + batch_size, n)
+            x = test_data[i:hi]
+            x = as_token_ids(x) if np.issubdtype(np.asarray(x).dtype, np.integer) else as_device(np.asarray(x, dtype=np.float32))
+            y_hat = self.predict(x)
+            V = y_hat.shape[-1]
+            rows = y_hat.size // V
+            y = as_token_ids(np.ascontiguousarray(labels[i:hi]).reshape(rows))
+            check(lib.tlnn_eval_batch_fwd(backend.ctx(), y_hat.ptr, V, y.ptr, _ids_code(y), rows, V, acc.ptr, acc.ptr + 8))
+        host = acc.get()
+        total = float(np.prod(labels.shape))
+        return float(host[:8].view(np.float64)[0]) / total, float(host[8:].view(np.int64)[0]) / total
 
     def generate(self, seed_tokens, length: int, uniforms=None, seed=None, use_cache: bool = True):
         """The notebook's ``GPT.generate`` (demo.ipynb:1520-1535) for every row of ``seed_tokens``: each step crops
