@@ -65,3 +65,25 @@ def test_label_out_of_range_is_an_index_error(engine):
     with pytest.raises(IndexError):
         CrossEntropy(10).loss(p, np.array([1, 2, 10, 3]))
         backend.synchronize()
+
+
+def test_prefetched_batches_equal_plain_uploads(engine, golden):
+    """The double-buffered feeder delivers every batch (ragged last one included) bit for bit, and evaluate gives the
+    same two numbers with and without it."""
+    from torchless_nn_b200.host_feed import HostFeed
+    from torchless_nn_b200.network import CrossEntropy
+    g = golden("eval_tiny")
+    engine.set_precision("tf32")
+    data = g["images"]
+    per = int(np.prod(data.shape[1:])) * 4
+    with HostFeed(per * 8) as feed:
+        seen = []
+        for lo, hi, dev in feed.batches(data, 8, np.float32):
+            assert dev.shape == data[lo:hi].shape
+            assert np.array_equal(dev.get(), data[lo:hi])
+            seen.append((lo, hi))
+    assert seen == [(0, 8), (8, 16), (16, 20)]
+    net = _build(g)
+    a = net.evaluate(data, g["labels"], CrossEntropy(10), batch_size=8, prefetch=True)
+    b = net.evaluate(data, g["labels"], CrossEntropy(10), batch_size=8, prefetch=False)
+    assert a == b

@@ -152,27 +152,49 @@ class Network:
             return tokens
         return argmax_last(self.predict(input))
 
-    def evaluate(self, test_data, test_labels, criterion=None, batch_size=64):
+    def evaluate(self, test_data, test_labels, criterion=None, batch_size=64, prefetch=True):
         """network.py:145-160: mean cross-entropy and accuracy of ``predict`` over ``test_data`` in batches.  The
         arg-max, its comparison with the labels and the loss terms stay on the device; two numbers come back at the
-        end.  ``criterion`` is accepted for signature compatibility (its ``loss`` is what is computed)."""
+        end.  ``criterion`` is accepted for signature compatibility (its ``loss`` is what is computed).  With
+        ``prefetch`` the next batch is copied from pinned host memory on a second stream while the current one is
+        computed (the reference uploads each batch synchronously, network.py:152)."""
+        from .host_feed import HostFeed
         self.set_eval(True)
         n = len(test_data)
         labels = np.asarray(test_labels)
         acc = DeviceArray((16,), np.uint8)
         check(lib.tlnn_memset(backend.ctx(), acc.ptr, 0, 16))
-        for i in range(0, n, batch_size):
-            hi = min(i + batch_size, n)
-            x = test_data[i:hi]
-            x = as_token_ids(x) if np.issubdtype(np.asarray(x).dtype, np.integer) else as_device(np.asarray(x, dtype=np.float32))
-            y_hat = self.predict(x)
-            V = y_hat.shape[-1]
-            rows = y_hat.size // V
-            y = as_token_ids(np.ascontiguousarray(labels[i:hi]).reshape(rows))
-            check(lib.tlnn_eval_batch_fwd(backend.ctx(), y_hat.ptr, V, y.ptr, _ids_code(y), rows, V, acc.ptr, acc.ptr + 8))
+        first = np.asarray(test_data[0:1])
+        is_ids = np.issubdtype(first.dtype, np.integer)
+        in_dtype = (first.dtype if first.dtype in (np.dtype(np.int32), np.dtype(np.uint8), np.dtype(np.int64)) else np.dtype(np.int64)) \
+            if is_ids else np.dtype(np.float32)
+
+        def plain():
+            for i in range(0, n, batch_size):
+                hi = min(i + batch_size, n)
+                x = np.asarray(test_data[i:hi], dtype=in_dtype)
+                yield i, hi, (as_token_ids(x) if is_ids else as_device(x))
+
+        feed = HostFeed(int(np.prod(first.shape[1:])) * in_dtype.itemsize * batch_size) if (prefetch and n > 0) else None
+        source = feed.batches(test_data, batch_size, in_dtype) if feed else plain()
+        try:
+            for i, hi, x in source:
+                self._evaluate_batch(x, labels[i:hi], acc)
+        finally:
+            if feed:
+                backend.synchronize()
+                feed.close()
         host = acc.get()
         total = float(np.prod(labels.shape))
         return float(host[:8].view(np.float64)[0]) / total, float(host[8:].view(np.int64)[0]) / total
+
+    def _evaluate_batch(self, x, batch_labels, acc):
+        """One batch of ``evaluate``: forward, then loss terms and correct arg-max count added on the device."""
+        y_hat = self.predict(x)
+        V = y_hat.shape[-1]
+        rows = y_hat.size // V
+        y = as_token_ids(np.ascontiguousarray(batch_labels).reshape(rows))
+        check(lib.tlnn_eval_batch_fwd(backend.ctx(), y_hat.ptr, V, y.ptr, _ids_code(y), rows, V, acc.ptr, acc.ptr + 8))
 
     def generate(self, seed_tokens, length: int, uniforms=None, seed=None, use_cache: bool = True):
         """The notebook's ``GPT.generate`` (demo.ipynb:1520-1535) for every row of ``seed_tokens``: each step crops
