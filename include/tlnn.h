@@ -248,6 +248,13 @@ int tlnn_feed_acquire(tlnn_feeder* f, int slot, void** dev);
 int tlnn_feed_release(tlnn_feeder* f, int slot);
 int tlnn_feed_destroy(tlnn_feeder* f);
 
+/* ---- failure handling self-test ------------------------------------------ */
+/* No counterpart in the reference.  Every device-side wait of the library (TMA, tensor-core and hand-over barriers)
+ * goes through one bounded-wait routine; this call launches a one-thread kernel that waits, through that routine, on
+ * a barrier nothing arrives at, with a limit of limit_ms (1..1000).  The kernel returns normally; the next
+ * tlnn_sync / tlnn_check reports TLNN_ERR_TIMEOUT, after which the context is clean and usable again. */
+int tlnn_selftest_wait(tlnn_ctx* ctx, int limit_ms);
+
 /* ---- profiling -------------------------------------------------------------- */
 /* CUDA-event timing of everything enqueued between begin and end on the compute stream (milliseconds). */
 int tlnn_prof_begin(tlnn_ctx* ctx);

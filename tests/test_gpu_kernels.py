@@ -355,3 +355,31 @@ def test_device_array_api(engine):
     assert np.array_equal(np.asarray(d), a)
     z = xp.zeros((3, 2))
     assert np.all(z.get() == 0)
+
+
+# ----------------------------------------------------------------------------- failure handling
+def test_expired_wait_is_reported_and_the_context_survives(engine):
+    """A device-side wait that nothing satisfies gives up after its limit (60 ms here), the kernel returns, the next
+    synchronisation raises RuntimeError with the time-out status, and the same context computes correctly afterwards."""
+    import time
+    from torchless_nn_b200 import backend
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.layers import Dense
+    engine.set_precision("bf16")
+    try:
+        backend.synchronize()
+        t0 = time.time()
+        check(lib.tlnn_selftest_wait(backend.ctx(), 60))
+        with pytest.raises(RuntimeError) as info:
+            backend.synchronize()
+        assert time.time() - t0 < 5.0
+        assert "status -5" in str(info.value) and "site 900" in str(info.value)      # TLNN_ERR_TIMEOUT from the self-test
+        backend.synchronize()                       # the error has been consumed
+        layer = Dense(64, 32)
+        x = np.random.default_rng(0).standard_normal((50, 64), dtype=np.float32)
+        w = np.random.default_rng(1).standard_normal((64, 32), dtype=np.float32) / 8
+        _load(w, layer.weights)
+        _load(np.zeros(32, dtype=np.float32), layer.bias)
+        assert rel_err(layer.forward(x).get(), x @ w) < TOL["bf16"]
+    finally:
+        engine.set_precision("tf32")

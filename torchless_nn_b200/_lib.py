@@ -77,6 +77,7 @@ PROTOTYPES = {
     "tlnn_feed_acquire": (C.c_int, [vp, C.c_int, C.POINTER(vp)]),
     "tlnn_feed_release": (C.c_int, [vp, C.c_int]),
     "tlnn_feed_destroy": (C.c_int, [vp]),
+    "tlnn_selftest_wait": (C.c_int, [vp, C.c_int]),
     "tlnn_eval_batch_fwd": (C.c_int, [vp, vp, ll, vp, C.c_int, ll, C.c_int, vp, vp]),
     "tlnn_attention_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tlnn_ffn_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, C.c_int, vp, ll, C.c_int]),

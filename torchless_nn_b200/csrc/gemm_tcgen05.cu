@@ -844,6 +844,29 @@ int launch_bn(tlnn_ctx* ctx, bool tf32, int mode, const CUtensorMap& ta, const C
 
 }  // namespace
 
+namespace {
+// A wait that nothing will satisfy, through the same bounded-wait routine every kernel of the library uses: it gives
+// up after limit_ns, records TLNN_ERR_TIMEOUT and the kernel returns normally.
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, tlnn_dev_err* err) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait(&bar, 0, &abort_flag, err, 900, limit_ns);
+    }
+}
+}  // namespace
+
+extern "C" int tlnn_selftest_wait(tlnn_ctx* ctx, int limit_ms) {
+    TL_NOTNULL(ctx);
+    TL_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, "selftest: the wait limit must lie between 1 and 1000 ms");
+    TL_CUDA(cudaSetDevice(ctx->device));
+    TL_LAUNCH(ctx, "wait_selftest", wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>((unsigned long long)limit_ms * 1000000ull, ctx->d_err));
+    return TLNN_OK;
+}
+
 int tl_gemm_bn(int M, int N, int sm_count) { return pick_bn(M, N, sm_count); }
 int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count) {
     const int bn = use_pair(sm_count, prec, M, N) ? PairCfg::BN : pick_bn(M, N, sm_count);

@@ -79,13 +79,13 @@ static __device__ __forceinline__ bool mbar_wait_slow(
 static __device__ __noinline__ bool mbar_wait_slow(
 #endif
     uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            tlnn_dev_err* err, int site) {
+                                            tlnn_dev_err* err, int site, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     unsigned long long t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 128; i++)
             if (mbar_try_wait_hint(bar, parity, TLNN_WAIT_HINT_NS)) return true;
         if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             tl_dev_fail(err, TLNN_ERR_TIMEOUT, site, (long long)blockIdx.x);
             return false;
@@ -93,9 +93,9 @@ static __device__ __noinline__ bool mbar_wait_slow(
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          tlnn_dev_err* err, int site) {
+                                          tlnn_dev_err* err, int site, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, err, site);
+    return mbar_wait_slow(bar, parity, abort_flag, err, site, limit_ns);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
