@@ -151,7 +151,7 @@ enum {
     EPI_F32_RES = 3,     // float32 out (+bias) + float32 residual     same conditions, residual rows aligned too
     EPI_ARGMAX = 4,      // no output, (+bias), per-row arg-max candidates; ragged N allowed
     EPI_F32_ACCUM = 5,   // out += acc (+bias): the residual IS the output buffer (in-place residual stream)
-    EPI_F32 = 6          // float32 out (+bias), no activation, no residual
+    EPI_F32 = 6          // float32 out (+bias, +activation, optionally rounded to TF32), no residual
 };
 // EPI_BF16, EPI_BF16_GELU, EPI_F32 and EPI_F32_ACCUM leave the tile through TMA: the warp writes its 32-row slab into its
 // staging tile in the 128-byte-swizzled layout and one lane issues a bulk tensor store (bf16: 64 columns at a time) or a
@@ -199,7 +199,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
     const bool want_argmax = MODE == EPI_ARGMAX || (GENERIC && ep.argmax_partials != nullptr);
     const bool has_out = HAS_OUT && (!GENERIC || ep.out != nullptr);
     const bool out_bf16 = MODE == EPI_BF16 || MODE == EPI_BF16_GELU || (GENERIC && ep.out_kind == TL_OUT_BF16);
-    const bool round_out = GENERIC && ep.out_kind == TL_OUT_TF32;
+    const bool round_out = (GENERIC || MODE == EPI_F32) && ep.out_kind == TL_OUT_TF32;
     bool vec_ok = true;                              // specialised variants: guaranteed by the host
     if (GENERIC) {
         const int esz = out_bf16 ? 2 : 4;
@@ -289,7 +289,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
             }
             if (MODE == EPI_BF16_GELU) {
                 apply_act_chunk<false>(TLNN_ACT_GELU, v);
-            } else if (GENERIC && ep.act != TLNN_ACT_NONE) {
+            } else if ((GENERIC || MODE == EPI_F32) && ep.act != TLNN_ACT_NONE) {
                 if (ep.accurate_math) apply_act_chunk<true>(ep.act, v);
                 else apply_act_chunk<false>(ep.act, v);
             }
@@ -318,6 +318,10 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                         *reinterpret_cast<uint4*>(row + ((((i & 1) * 4 + u) ^ (lane & 7)) << 4)) = pk;
                     }
                 } else {
+                    if (MODE == EPI_F32 && round_out) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = round_tf32(v[j]);
+                    }
 #pragma unroll
                     for (int u = 0; u < 8; u++)
                         *reinterpret_cast<float4*>(stage_tile + lane * 32 + ((u ^ (lane & 7)) << 2)) =
@@ -812,7 +816,8 @@ int pick_mode(const tl_gemm_epilogue& ep, int N) {
         if (ep.act == TLNN_ACT_NONE) return EPI_BF16;
         if (ep.act == TLNN_ACT_GELU && !ep.accurate_math) return EPI_BF16_GELU;
     }
-    if (ep.out_kind == TL_OUT_F32 && ep.residual == nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0)
+    // float32 out (as is, or rounded to TF32 for the next product), optional activation, no residual
+    if ((ep.out_kind == TL_OUT_F32 || ep.out_kind == TL_OUT_TF32) && ep.residual == nullptr && (ep.ldo * 4) % 16 == 0)
         return EPI_F32;
     if (ep.out_kind == TL_OUT_F32 && ep.residual != nullptr && ep.act == TLNN_ACT_NONE && (ep.ldo * 4) % 16 == 0 &&
         aligned16(ep.residual) && ep.ldr % 4 == 0)
