@@ -9,6 +9,7 @@
 #include <string>
 #include <vector>
 #include <map>
+#include <utility>
 
 #include "../../include/tlnn.h"
 
@@ -43,6 +44,7 @@ struct tlnn_ctx {
     tlnn_dev_err* h_err = nullptr;     // pinned host mirror
     int* d_sched = nullptr;            // device work counter of the persistent attention kernel (zeroed per launch)
     long long launches = 0;
+    bool pdl = false;                  // launches made now may start before their predecessor has finished (see tl_launch_kernel)
     void* prefill_cache = nullptr;     // captured graph of the last repeated tlnn_gpt_prefill call (layers.cu)
     // grow-only scratch arena used by the composite layer calls (stream-ordered reuse)
     char* ws = nullptr;
@@ -101,6 +103,32 @@ int tl_launch_end(tlnn_ctx* ctx, const char* name);
     } while (0)
 
 void tl_prefill_cache_free(tlnn_ctx* ctx);     // layers.cu: drops the captured prefill graph
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// A kernel that begins with tl_grid_dependency_sync() may be launched while its predecessor in the stream is still
+// running: the call lets the kernel's own successor start launching, then waits until every predecessor grid has
+// completed and its memory is visible.  Launch latency and whatever the kernel does before the call (barrier set-up,
+// TMEM allocation) overlap with the predecessor.  Without the launch attribute both instructions do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void tl_grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void tl_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void tl_grid_dependency_sync() { tl_grid_dependency_trigger(); tl_grid_dependency_wait(); }
+
+template <typename... KArgs, typename... Args>
+inline void tl_launch_kernel(tlnn_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);      // the launch status is read by tl_launch_end
+}
+#endif
 
 // ---- scratch arena ---------------------------------------------------------------------------------
 // A composite call reserves its total need up front (which may reallocate while the stream is idle), then

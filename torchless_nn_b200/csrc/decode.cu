@@ -7,6 +7,7 @@
 // GEMM with fused arg-max.  The step is weight-streaming (HBM) bound.  The current length lives in device memory and
 // every kernel of a step reads it from there, so the launch sequence of a step does not depend on the position.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -48,6 +49,7 @@ __global__ void kv_store_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E
 __global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const float* __restrict__ table,
                                     const float* __restrict__ pos, const int* __restrict__ len, float* __restrict__ out,
                                     int B, int d, int vocab, tlnn_dev_err* err) {
+    tl_grid_dependency_sync();
     const int b = blockIdx.x;
     long long id = tokens[b];
     if (id < 0 || id >= vocab) {
@@ -73,6 +75,7 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
     float* sc = sm;                                // cache_len scores / probabilities
     __shared__ float red[8];
     __shared__ float part[128 * PER];              // KPP x HD partial outputs
+    tl_grid_dependency_sync();
     const int d = H * HD;
     const int b = blockIdx.x / H, h = blockIdx.x % H;
     const int pos = *len_ptr;
@@ -162,6 +165,7 @@ struct decode_sink {          // lives in device memory so that a captured step 
 
 __global__ void decode_advance_kernel(const int32_t* __restrict__ next, int32_t* __restrict__ cur,
                                       const decode_sink* __restrict__ sink, int* len, int* step, int B) {
+    tl_grid_dependency_sync();
     const int s = *step;
     int32_t* tokens_out = sink->tokens_out;
     const int n_cols = sink->n_cols;
@@ -229,7 +233,7 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
     const size_t smem = (size_t)dec->max_len * sizeof(float);
     const int round_out = dec->m.prec == TLNN_PREC_TF32;
 #define DA_CASE(E, HDV)                                                                                              \
-    TL_LAUNCH(ctx, "decode_attention", decode_attention_kernel<E, HDV><<<B * H, 128, smem, ctx->stream>>>(           \
+    TL_LAUNCH(ctx, "decode_attention", tl_launch_kernel(ctx, decode_attention_kernel<E, HDV>, dim3(B * H), dim3(128), smem, \
                   (const E*)dec->qkv, (E*)dec->kcache + layer * layer_elems, (E*)dec->vcache + layer * layer_elems, \
                   (E*)dec->att, dec->d_len, H, dec->max_len, inv, round_out))
     if (dec->m.prec == TLNN_PREC_BF16) {
@@ -250,8 +254,16 @@ int decode_one(tlnn_decoder* dec, bool sample = false, float temperature = 1.f) 
     tlnn_ctx* ctx = dec->ctx;
     const tlnn_gpt_model& m = dec->m;
     const int B = dec->B, d = m.d, prec = m.prec, kind = okind(prec);
-    TL_LAUNCH(ctx, "decode_embed", decode_embed_kernel<<<B, 128, 0, ctx->stream>>>(dec->cur, m.tok_table, m.pos_table,
-                                                                                   dec->d_len, dec->x0, B, d, m.vocab, ctx->d_err));
+    // Inside a step every kernel may be launched while its predecessor still runs (each starts with a grid-dependency
+    // wait): a step is 89 dependent kernels of 5-15 us, and launch latency is a large part of it.  TLNN_PDL=0 disables.
+    static const bool pdl_allowed = !(getenv("TLNN_PDL") && strcmp(getenv("TLNN_PDL"), "0") == 0);
+    struct pdl_scope {
+        tlnn_ctx* c; bool old;
+        pdl_scope(tlnn_ctx* cc, bool on) : c(cc), old(cc->pdl) { c->pdl = on; }
+        ~pdl_scope() { c->pdl = old; }
+    } scope(ctx, pdl_allowed && !ctx->prof_classes);
+    TL_LAUNCH(ctx, "decode_embed", tl_launch_kernel(ctx, decode_embed_kernel, dim3(B), dim3(128), 0, dec->cur, m.tok_table, m.pos_table,
+                                                    dec->d_len, dec->x0, B, d, m.vocab, ctx->d_err));
     float* x = dec->x0;
     float* xn = dec->x1;
     for (int l = 0; l < m.layers; l++) {
@@ -291,8 +303,8 @@ int decode_one(tlnn_decoder* dec, bool sample = false, float temperature = 1.f) 
         TL_TRY(tl_gemm(ctx, prec, dec->a, d, m.head_t, d, B, m.vocab, d, eh));
         TL_TRY(tl_argmax_partials(ctx, dec->parts, dec->n_parts, dec->next, B));
     }
-    TL_LAUNCH(ctx, "decode_advance", decode_advance_kernel<<<1, 256, 0, ctx->stream>>>(dec->next, dec->cur, dec->d_sink,
-                                                                                      dec->d_len, dec->d_step, B));
+    TL_LAUNCH(ctx, "decode_advance", tl_launch_kernel(ctx, decode_advance_kernel, dim3(1), dim3(256), 0, dec->next, dec->cur, dec->d_sink,
+                                                      dec->d_len, dec->d_step, B));
     return TLNN_OK;
 }
 

@@ -437,6 +437,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    tl_grid_dependency_trigger();            // the successor may start launching; it waits for this grid itself
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = m_tiles * n_tiles;
@@ -469,6 +470,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers, TMEM and descriptors are ready; nothing below may touch global memory before the predecessor is done
+    tl_grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -735,8 +738,8 @@ int launch(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CU
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     const char* name = TF32 ? (BN == 256 ? "gemm_tf32_n256" : BN == 128 ? "gemm_tf32_n128" : "gemm_tf32_n64")
                             : (BN == 256 ? "gemm_bf16_n256" : BN == 128 ? "gemm_bf16_n128" : "gemm_bf16_n64");
-    TL_LAUNCH(ctx, name, kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM, ctx->stream>>>(ta, tb, to, ep, M, N, K, m_tiles, n_tiles,
-                                                                                   split_k, ctx->d_err));
+    TL_LAUNCH(ctx, name, tl_launch_kernel(ctx, kernel, dim3(grid), dim3(NUM_THREADS), Cfg<BN>::SMEM, ta, tb, to, ep, M, N, K, m_tiles,
+                                          n_tiles, split_k, ctx->d_err));
     return TLNN_OK;
 }
 

@@ -92,6 +92,7 @@ template <int KIND, int VPL /* float4 per lane */>
 __global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                       const float* __restrict__ beta, float eps, void* __restrict__ out,
                                       long long rows, int d) {
+    tl_grid_dependency_sync();
     long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
     int lane = threadIdx.x % kWarp;
     if (row >= rows) return;
@@ -230,6 +231,7 @@ __global__ void transpose_convert_kernel(const float* __restrict__ w, int rows, 
 __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ out, int cols, float temperature) {
     __shared__ float red[32];
     __shared__ float bcast;
+    tl_grid_dependency_sync();
     const float* src = x + (long long)blockIdx.x * cols;
     float* dst = out + (long long)blockIdx.x * cols;
     int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarp = blockDim.x / kWarp;
@@ -300,6 +302,7 @@ __global__ void argmax_kernel(const float* __restrict__ x, long long ldx, int32_
 // Reduce the per-tile (max, index) pairs a GEMM epilogue left behind: one warp per row.
 __global__ void argmax_partials_kernel(const float2* __restrict__ parts, int n_parts, int32_t* __restrict__ out,
                                        long long rows) {
+    tl_grid_dependency_sync();
     long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
     int lane = threadIdx.x % kWarp;
     if (row >= rows) return;
@@ -394,8 +397,8 @@ static int layernorm_dispatch(tlnn_ctx* ctx, const float* x, const float* gamma,
         unsigned grid = (unsigned)((rows + warps - 1) / warps);
         int vpl = (d / 4 + 31) / 32;
 #define LN_CASE(V)                                                                                              \
-    TL_LAUNCH(ctx, "layernorm", layernorm_warp_kernel<KIND, V><<<grid, warps * 32, 0, ctx->stream>>>(          \
-                  x, gamma, beta, eps, out, rows, d))
+    TL_LAUNCH(ctx, "layernorm", tl_launch_kernel(ctx, layernorm_warp_kernel<KIND, V>, dim3(grid), dim3(warps * 32), 0, \
+                                                 x, gamma, beta, eps, out, rows, d))
         if (vpl <= 1) LN_CASE(1);
         else if (vpl <= 2) LN_CASE(2);
         else if (vpl <= 4) LN_CASE(4);
@@ -439,7 +442,7 @@ int tl_argmax_partials(tlnn_ctx* ctx, const float2* partials, int n_parts, int32
     const int warps = 8;
     unsigned grid = (unsigned)((rows + warps - 1) / warps);
     TL_LAUNCH(ctx, "argmax_partials",
-              argmax_partials_kernel<<<grid, warps * 32, 0, ctx->stream>>>(partials, n_parts, tokens, rows));
+              tl_launch_kernel(ctx, argmax_partials_kernel, dim3(grid), dim3(warps * 32), 0, partials, n_parts, tokens, rows));
     return TLNN_OK;
 }
 
@@ -479,7 +482,7 @@ extern "C" int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long 
     TL_NOTNULL(x); TL_NOTNULL(out);
     TL_CUDA(cudaSetDevice(ctx->device));
     int block = cols >= 8192 ? 1024 : (cols >= 1024 ? 256 : 64);
-    TL_LAUNCH(ctx, "softmax", softmax_kernel<<<(unsigned)rows, block, 0, ctx->stream>>>(x, out, cols, temperature));
+    TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_kernel, dim3((unsigned)rows), dim3(block), 0, x, out, cols, temperature));
     return TLNN_OK;
 }
 
@@ -493,6 +496,7 @@ __global__ void __launch_bounds__(256) sample_kernel(const float* __restrict__ p
                                                      const int* __restrict__ step, int32_t* __restrict__ out, int cols) {
     __shared__ double seg[256];
     __shared__ int found;
+    tl_grid_dependency_sync();
     const long long row = blockIdx.x;
     const float* p = probs + row * ldp;
     const int per = (cols + 255) / 256;
@@ -522,7 +526,7 @@ __global__ void __launch_bounds__(256) sample_kernel(const float* __restrict__ p
 
 int tl_sample(tlnn_ctx* ctx, const float* probs, long long ldp, const double* uniforms, const int* step, int32_t* out,
               long long rows, int cols) {
-    TL_LAUNCH(ctx, "sample", sample_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(probs, ldp, uniforms, step, out, cols));
+    TL_LAUNCH(ctx, "sample", tl_launch_kernel(ctx, sample_kernel, dim3((unsigned)rows), dim3(256), 0, probs, ldp, uniforms, step, out, cols));
     return TLNN_OK;
 }
 
