@@ -46,7 +46,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # in profiles/gemm_tcgen05_c3_prefill.md (c3: 16384 rows, width 768): 411.7 MB.  Traffic grows with rows x width, so a
 # workload's mean launch is estimated as that figure scaled by (rows x width) / (16384 x 768), times layers, plus the
 # head's operand and arg-max candidate bytes, over the number of GEMM launches.
-GEMM_BLOCK_TRAFFIC_C3 = 411.7e6
+GEMM_BLOCK_TRAFFIC_C3 = 374.8e6
 
 
 def measured_peak():
