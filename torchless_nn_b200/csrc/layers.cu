@@ -338,6 +338,14 @@ namespace {
 int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T, float* logits,
                     int32_t* tokens) {
     const long long M = (long long)B * T;
+    // Kernels that begin with a grid-dependency wait (LayerNorm, the one-CTA GEMM, the arg-max reduction) may be launched
+    // while their predecessor still runs; the others are launched plainly and serialise as usual.  TLNN_PDL_PREFILL=1.
+    static const bool pdl_allowed = getenv("TLNN_PDL_PREFILL") && strcmp(getenv("TLNN_PDL_PREFILL"), "1") == 0;
+    struct pdl_scope {
+        tlnn_ctx* c; bool old;
+        pdl_scope(tlnn_ctx* cc, bool on) : c(cc), old(cc->pdl) { c->pdl = on; }
+        ~pdl_scope() { c->pdl = old; }
+    } scope(ctx, pdl_allowed && !ctx->prof_classes);
     const int d = m->d;
     const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
     const size_t tail = block_ws_bytes(m->prec, M, d);
