@@ -255,19 +255,22 @@ def test_attention_long_and_ragged(engine, prec, B, T, d, H, causal):
     assert rel_err(y, ref) < TOL[prec]
 
 
-@pytest.mark.parametrize("B,T,d,H,causal", [(2, 50, 32, 2, True), (3, 33, 32, 4, False), (1, 130, 64, 4, True)])
+@pytest.mark.parametrize("B,T,d,H,causal", [(2, 50, 32, 2, True), (3, 33, 32, 4, False), (1, 130, 64, 4, True),
+                                            (2, 65, 64, 2, False), (2, 65, 64, 2, True), (1, 257, 64, 2, False),
+                                            (2, 100, 128, 2, True), (1, 36, 64, 1, False), (1, 132, 128, 2, False)])
 def test_attention_small_heads_float32(engine, B, T, d, H, causal):
-    """Head dimensions 8 and 16 exist in float32 / TF32 mode only (thread-per-query kernel)."""
+    """Head dimensions 8 and 16 exist in float32 / TF32 mode only (thread-per-query kernel); lengths one to four past a
+    multiple of 32 (a ViT's class token) send their last queries to the warp-per-query rows of that kernel."""
     from torchless_nn_b200.layers import MultiHeadAttention
     engine.set_precision("tf32")
     rng = np.random.default_rng(T + d + H)
-    at = MultiHeadAttention(d, 256, H, decoder=causal)
+    at = MultiHeadAttention(d, max(256, T), H, decoder=causal)
     ws = [rng.standard_normal(p.shape, dtype=np.float32) * np.float32(0.1) for p in at.parameters]
     for p, w in zip(at.parameters, ws):
         _load(w, p)
     x = rng.standard_normal((B, T, d), dtype=np.float32)
     y = at.forward(x).get()
-    ref = onp.attention(x, *ws, H, onp.causal_mask(256) if causal else None)
+    ref = onp.attention(x, *ws, H, onp.causal_mask(max(256, T)) if causal else None)
     assert rel_err(y, ref) < TOL["tf32"]
 
 

@@ -333,16 +333,76 @@ attention_f32_kernel(const float* __restrict__ qkv, float* __restrict__ out, int
     }
 }
 
-// Float32 attention, one thread per query (head dimension 32 or 64).  The query row, the running maximum, the row sum
-// and the output row live in registers; key and value rows are read from shared memory as broadcasts (every thread of
-// a warp reads the same 16 bytes), so a key costs 2 HD / 4 shared loads per thread for 2 HD multiply-adds and nothing
-// is exchanged between threads.  Keys are taken eight at a time: eight scores, one maximum update and one rescale of
-// the output row, then eight exponentials.  Exact float32 arithmetic and libm-grade expf keep the 2e-3 budget of the
-// float32 / TF32 mode.
+// Queries past the last full warp (T_main <= qi < T), one warp per query: the lanes split the keys for the scores and
+// the output columns for the weighted sum of value rows, both read straight from global memory (the row threads of the
+// neighbouring CTAs have just pulled the same rows through L2).  Two passes over the keys: the row maximum first, then
+// exponentials and the weighted sum 32 keys at a time, so nothing per key is kept.
+template <int HD, bool CAUSAL>
+__device__ __forceinline__ void attention_f32_tail_rows(const float* __restrict__ qbase, const float* __restrict__ kbase,
+                                                        const float* __restrict__ vbase, float* __restrict__ out_bh,
+                                                        int T, int T_main, int d, long long row_stride,
+                                                        float inv_sqrt_hd, int round_out) {
+    constexpr int V4 = HD / 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int qi = T_main + warp; qi < T; qi += nwarps) {
+        float q[HD];
+#pragma unroll
+        for (int c = 0; c < V4; c++) {
+            const float4 t = *reinterpret_cast<const float4*>(qbase + (long long)qi * row_stride + 4 * c);
+            q[4 * c] = t.x; q[4 * c + 1] = t.y; q[4 * c + 2] = t.z; q[4 * c + 3] = t.w;
+        }
+        auto score = [&](int key) {
+            const float* kr = kbase + (long long)key * row_stride;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int c = 0; c < V4; c++) {
+                const float4 kv = *reinterpret_cast<const float4*>(kr + 4 * c);
+                a0 = fmaf(q[4 * c], kv.x, a0); a1 = fmaf(q[4 * c + 1], kv.y, a1);
+                a2 = fmaf(q[4 * c + 2], kv.z, a2); a3 = fmaf(q[4 * c + 3], kv.w, a3);
+            }
+            return ((a0 + a1) + (a2 + a3)) * inv_sqrt_hd;
+        };
+        const int nkeys = CAUSAL ? qi + 1 : T;
+        float mx = -INFINITY;
+        for (int key = lane; key < nkeys; key += 32) mx = fmaxf(mx, score(key));
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        float l = 0.f, o0 = 0.f, o1 = 0.f;                 // output columns lane and lane + 32
+        for (int k0 = 0; k0 < nkeys; k0 += 32) {
+            const int key = k0 + lane;
+            const float p = key < nkeys ? expf(score(key) - mx) : 0.f;
+            l += p;
+            const int cnt = min(32, nkeys - k0);
+#pragma unroll 8
+            for (int kk = 0; kk < cnt; kk++) {
+                const float pk = __shfl_sync(0xffffffffu, p, kk);
+                const float* vr = vbase + (long long)(k0 + kk) * row_stride;
+                if (lane < HD) o0 = fmaf(pk, vr[lane], o0);
+                if (HD > 32) o1 = fmaf(pk, vr[(lane + 32) % HD], o1);
+            }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) l += __shfl_xor_sync(0xffffffffu, l, s);
+        float* op = out_bh + (long long)qi * d;
+        if (lane < HD) { const float v = o0 / l; op[lane] = round_out ? round_tf32(v) : v; }
+        if (HD > 32) { const float v = o1 / l; op[(lane + 32) % HD] = round_out ? round_tf32(v) : v; }
+    }
+}
+
+// Float32 attention with the queries in registers (head dimension 8 to 64): a thread owns a query, its running
+// maximum, row sum and output row; key and value rows are read from shared memory as broadcasts (every thread of a
+// warp reads the same 16 bytes) and nothing is exchanged between threads.  Keys are taken eight at a time: eight
+// scores, one maximum update and one rescale of the output row, then eight exponentials.  Exact float32 arithmetic and
+// libm-grade expf keep the 2e-3 budget of the float32 / TF32 mode.  QPT (adjacent queries per thread) stays at 1: with
+// two, a shared-memory load feeds twice the multiply-adds, but the halved warp count cost more than that gained
+// (256 images of 65 tokens, 6 heads of 32: 1.27 ms per forward against 1.12 ms).
+// T_main is the number of queries the row threads take; when it is below T the last CTA of each (batch, head) column
+// handles the remaining T - T_main queries with attention_f32_tail_rows instead.
 template <int HD, bool CAUSAL>
 __global__ void __launch_bounds__(128)
-attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict__ out, int T, int H, float inv_sqrt_hd,
-                               int round_out) {
+attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict__ out, int T, int T_main, int H,
+                               float inv_sqrt_hd, int round_out) {
+    constexpr int QPT = 1;
     constexpr int KT = 64;                         // keys per shared-memory tile
     constexpr int V4 = HD / 4;
     __shared__ __align__(16) float sK[KT][HD];
@@ -351,26 +411,35 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
     const int d = H * HD;
     const long long row_stride = 3ll * d;
     const int bh = blockIdx.y, b = bh / H, h = bh % H;
-    const int q0 = blockIdx.x * blockDim.x;
-    const int qi = q0 + threadIdx.x;
-    const bool active = qi < T;
+    const int q0 = blockIdx.x * blockDim.x * QPT;
+    const int qi = q0 + threadIdx.x * QPT;           // first of this thread's queries; T_main is a multiple of QPT
+    const bool active = qi < T_main;
     const float* qbase = qkv + (long long)b * T * row_stride + h * HD;
     const float* kbase = qbase + d;
     const float* vbase = qbase + 2 * d;
-
-    float q[HD], o[HD];
-#pragma unroll
-    for (int c = 0; c < V4; c++) {
-        const float4 t = active ? *reinterpret_cast<const float4*>(qbase + (long long)qi * row_stride + 4 * c)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-        q[4 * c] = t.x; q[4 * c + 1] = t.y; q[4 * c + 2] = t.z; q[4 * c + 3] = t.w;
-        o[4 * c] = 0.f; o[4 * c + 1] = 0.f; o[4 * c + 2] = 0.f; o[4 * c + 3] = 0.f;
+    if (T_main < T && blockIdx.x == gridDim.x - 1) {               // uniform over the CTA, before any barrier
+        attention_f32_tail_rows<HD, CAUSAL>(qbase, kbase, vbase, out + (long long)b * T * d + h * HD, T, T_main, d,
+                                            row_stride, inv_sqrt_hd, round_out);
+        return;
     }
-    float m = -INFINITY, l = 0.f;
-    const int kv_end = CAUSAL ? min(T, q0 + (int)blockDim.x) : T;
+
+    float q[QPT][HD], o[QPT][HD], m[QPT], l[QPT];
+#pragma unroll
+    for (int j = 0; j < QPT; j++) {
+#pragma unroll
+        for (int c = 0; c < V4; c++) {
+            const float4 t = active ? *reinterpret_cast<const float4*>(qbase + (long long)(qi + j) * row_stride + 4 * c)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            q[j][4 * c] = t.x; q[j][4 * c + 1] = t.y; q[j][4 * c + 2] = t.z; q[j][4 * c + 3] = t.w;
+            o[j][4 * c] = 0.f; o[j][4 * c + 1] = 0.f; o[j][4 * c + 2] = 0.f; o[j][4 * c + 3] = 0.f;
+        }
+        m[j] = -INFINITY; l[j] = 0.f;
+    }
+    const int kv_end = CAUSAL ? min(T, q0 + (int)blockDim.x * QPT) : T;
     for (int k0 = 0; k0 < kv_end; k0 += KT) {
         __syncthreads();
-        for (int i = threadIdx.x; i < KT * V4; i += blockDim.x) {
+        const int tile_rows = min(KT, (kv_end - k0 + 7) & ~7);        // whole chunks of eight keys; rows past T are zeros
+        for (int i = threadIdx.x; i < tile_rows * V4; i += blockDim.x) {
             const int r = i / V4, c = i % V4;
             const bool ok = k0 + r < T;
             const long long off = (long long)(k0 + r) * row_stride + 4 * c;
@@ -381,49 +450,82 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
         if (!active) continue;
         const int nk = min(KT, kv_end - k0);
         for (int c0 = 0; c0 < nk; c0 += 8) {
-            if (CAUSAL && k0 + c0 > qi) break;                     // every later key is masked for this query
-            float sc[8];
+            if (CAUSAL && k0 + c0 > qi + QPT - 1) break;           // every later key is masked for these queries
+            const int cw = nk - c0;                                 // live keys of this chunk (uniform over the CTA)
+            float sc[QPT][8];
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                if (kk >= cw) {
+#pragma unroll
+                    for (int j = 0; j < QPT; j++) sc[j][kk] = -INFINITY;
+                    continue;
+                }
+                float a[QPT][4];
+#pragma unroll
+                for (int j = 0; j < QPT; j++) { a[j][0] = 0.f; a[j][1] = 0.f; a[j][2] = 0.f; a[j][3] = 0.f; }
 #pragma unroll
                 for (int c = 0; c < V4; c++) {
                     const float4 kv = *reinterpret_cast<const float4*>(&sK[c0 + kk][4 * c]);
-                    a0 = fmaf(q[4 * c], kv.x, a0); a1 = fmaf(q[4 * c + 1], kv.y, a1);
-                    a2 = fmaf(q[4 * c + 2], kv.z, a2); a3 = fmaf(q[4 * c + 3], kv.w, a3);
+#pragma unroll
+                    for (int j = 0; j < QPT; j++) {
+                        a[j][0] = fmaf(q[j][4 * c], kv.x, a[j][0]); a[j][1] = fmaf(q[j][4 * c + 1], kv.y, a[j][1]);
+                        a[j][2] = fmaf(q[j][4 * c + 2], kv.z, a[j][2]); a[j][3] = fmaf(q[j][4 * c + 3], kv.w, a[j][3]);
+                    }
                 }
                 const int key = k0 + c0 + kk;
-                const bool live = key < T && (!CAUSAL || key <= qi);
-                sc[kk] = live ? ((a0 + a1) + (a2 + a3)) * inv_sqrt_hd : -INFINITY;
-            }
-            float cm = fmaxf(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])), fmaxf(fmaxf(sc[4], sc[5]), fmaxf(sc[6], sc[7])));
-            const float mn = fmaxf(m, cm);
-            if (mn == -INFINITY) continue;                          // nothing visible yet
-            const float alpha = expf(m - mn);                        // 0 while m is still -inf
-            l *= alpha;
 #pragma unroll
-            for (int c = 0; c < HD; c++) o[c] *= alpha;
+                for (int j = 0; j < QPT; j++) {
+                    const bool live = key < T && (!CAUSAL || key <= qi + j);
+                    sc[j][kk] = live ? ((a[j][0] + a[j][1]) + (a[j][2] + a[j][3])) * inv_sqrt_hd : -INFINITY;
+                }
+            }
+            float mn[QPT];
+            bool any = false;
+#pragma unroll
+            for (int j = 0; j < QPT; j++) {
+                const float cm = fmaxf(fmaxf(fmaxf(sc[j][0], sc[j][1]), fmaxf(sc[j][2], sc[j][3])),
+                                       fmaxf(fmaxf(sc[j][4], sc[j][5]), fmaxf(sc[j][6], sc[j][7])));
+                mn[j] = fmaxf(m[j], cm);
+                // while nothing is visible yet the reference point stays finite, so every weight below is exp(-inf) = 0
+                const float ref = mn[j] == -INFINITY ? 0.f : mn[j];
+                const float alpha = expf(m[j] - ref);                // 0 while m is still -inf
+                any = any || mn[j] != -INFINITY;
+                l[j] *= alpha;
+#pragma unroll
+                for (int c = 0; c < HD; c++) o[j][c] *= alpha;
+                m[j] = mn[j];
+                mn[j] = ref;
+            }
+            if (!any) continue;
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
-                const float p = expf(sc[kk] - mn);                   // 0 for masked keys
-                l += p;
+                if (kk >= cw) break;
+                float p[QPT];
+#pragma unroll
+                for (int j = 0; j < QPT; j++) { p[j] = expf(sc[j][kk] - mn[j]); l[j] += p[j]; }   // 0 for masked keys
 #pragma unroll
                 for (int c = 0; c < V4; c++) {
                     const float4 vv = *reinterpret_cast<const float4*>(&sV[c0 + kk][4 * c]);
-                    o[4 * c] = fmaf(p, vv.x, o[4 * c]); o[4 * c + 1] = fmaf(p, vv.y, o[4 * c + 1]);
-                    o[4 * c + 2] = fmaf(p, vv.z, o[4 * c + 2]); o[4 * c + 3] = fmaf(p, vv.w, o[4 * c + 3]);
+#pragma unroll
+                    for (int j = 0; j < QPT; j++) {
+                        o[j][4 * c] = fmaf(p[j], vv.x, o[j][4 * c]); o[j][4 * c + 1] = fmaf(p[j], vv.y, o[j][4 * c + 1]);
+                        o[j][4 * c + 2] = fmaf(p[j], vv.z, o[j][4 * c + 2]); o[j][4 * c + 3] = fmaf(p[j], vv.w, o[j][4 * c + 3]);
+                    }
                 }
             }
-            m = mn;
         }
     }
     if (active) {
-        float* op = out + ((long long)b * T + qi) * d + h * HD;
 #pragma unroll
-        for (int c = 0; c < V4; c++) {
-            float4 r = make_float4(o[4 * c] / l, o[4 * c + 1] / l, o[4 * c + 2] / l, o[4 * c + 3] / l);
-            if (round_out) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
-            *reinterpret_cast<float4*>(op + 4 * c) = r;
+        for (int j = 0; j < QPT; j++) {
+            float* op = out + ((long long)b * T + qi + j) * d + h * HD;
+            const float inv_l = l[j];
+#pragma unroll
+            for (int c = 0; c < V4; c++) {
+                float4 r = make_float4(o[j][4 * c] / inv_l, o[j][4 * c + 1] / inv_l, o[j][4 * c + 2] / inv_l, o[j][4 * c + 3] / inv_l);
+                if (round_out) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
+                *reinterpret_cast<float4*>(op + 4 * c) = r;
+            }
         }
     }
 }
@@ -453,13 +555,21 @@ int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H,
     if constexpr (HD <= 64) {
         // the packed projection rows must allow 16-byte loads of a head's slice
         if ((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
-            const int threads = T >= 128 ? 128 : ((T + 31) / 32) * 32;
-            dim3 grid((T + threads - 1) / threads, B * H);
-            if (causal)
-                TL_LAUNCH(ctx, "attention_f32_causal", attention_f32_rowthread_kernel<HD, true><<<grid, threads, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
-            else
-                TL_LAUNCH(ctx, "attention_f32_full", attention_f32_rowthread_kernel<HD, false><<<grid, threads, 0, ctx->stream>>>(qkv, out, T, H, inv, round_out));
-            return TLNN_OK;
+            // A few queries past a warp boundary (a ViT's class token: 65, 257 rows) would cost a whole warp of row
+            // threads; they go to one extra CTA per (batch, head) that spends a warp per query instead.
+            const int rem = T % 32;
+            const int T_main = (T >= 32 && rem > 0 && rem <= 4) ? T - rem : T;
+            const int tail_cta = T_main < T ? 1 : 0;
+            const int threads = T_main >= 128 ? 128 : ((T_main + 31) / 32) * 32;
+            dim3 grid((T_main + threads - 1) / threads + tail_cta, B * H);
+            auto launch = [&](auto kern) -> int {
+                TL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+                TL_LAUNCH(ctx, causal ? "attention_f32_causal" : "attention_f32_full", kern<<<grid, threads, 0, ctx->stream>>>(qkv, out, T, T_main, H, inv, round_out));
+                return TLNN_OK;
+            };
+            // Tighter launch bounds (80 or 96 registers, so that all CTAs of the 65-token case are resident at once)
+            // were slower: the few spilled values sit in the key loop.
+            return causal ? launch(attention_f32_rowthread_kernel<HD, true>) : launch(attention_f32_rowthread_kernel<HD, false>);
         }
     }
     if constexpr (HD < 32) {
