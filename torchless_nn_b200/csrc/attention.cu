@@ -442,10 +442,12 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
         for (int i = threadIdx.x; i < tile_rows * V4; i += blockDim.x) {
             const int r = i / V4, c = i % V4;
             const bool ok = k0 + r < T;
-            const long long off = (long long)(k0 + r) * row_stride + 4 * c;
-            *reinterpret_cast<float4*>(&sK[r][4 * c]) = ok ? *reinterpret_cast<const float4*>(kbase + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4*>(&sV[r][4 * c]) = ok ? *reinterpret_cast<const float4*>(vbase + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const long long off = (long long)(ok ? k0 + r : 0) * row_stride + 4 * c;
+            cp_async16(smem_u32(&sK[r][4 * c]), kbase + off, ok);      // all of a thread's copies are in flight at once
+            cp_async16(smem_u32(&sV[r][4 * c]), vbase + off, ok);
         }
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
         if (!active) continue;
         const int nk = min(KT, kv_end - k0);
