@@ -257,10 +257,12 @@ def test_attention_long_and_ragged(engine, prec, B, T, d, H, causal):
 
 @pytest.mark.parametrize("B,T,d,H,causal", [(2, 50, 32, 2, True), (3, 33, 32, 4, False), (1, 130, 64, 4, True),
                                             (2, 65, 64, 2, False), (2, 65, 64, 2, True), (1, 257, 64, 2, False),
-                                            (2, 100, 128, 2, True), (1, 36, 64, 1, False), (1, 132, 128, 2, False)])
+                                            (2, 100, 128, 2, True), (1, 36, 64, 1, False), (1, 132, 128, 2, False),
+                                            (128, 65, 192, 6, False), (40, 128, 256, 8, True), (96, 40, 128, 8, True)])
 def test_attention_small_heads_float32(engine, B, T, d, H, causal):
     """Head dimensions 8 and 16 exist in float32 / TF32 mode only (thread-per-query kernel); lengths one to four past a
-    multiple of 32 (a ViT's class token) send their last queries to the warp-per-query rows of that kernel."""
+    multiple of 32 (a ViT's class token) send their last queries to the warp-per-query rows of that kernel.  The large
+    batches have enough warps for one thread per query; the others split each query's keys over four lanes."""
     from torchless_nn_b200.layers import MultiHeadAttention
     engine.set_precision("tf32")
     rng = np.random.default_rng(T + d + H)

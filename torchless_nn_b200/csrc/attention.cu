@@ -391,28 +391,35 @@ __device__ __forceinline__ void attention_f32_tail_rows(const float* __restrict_
 
 // Float32 attention with the queries in registers (head dimension 8 to 64): a thread owns a query, its running
 // maximum, row sum and output row; key and value rows are read from shared memory as broadcasts (every thread of a
-// warp reads the same 16 bytes) and nothing is exchanged between threads.  Keys are taken eight at a time: eight
-// scores, one maximum update and one rescale of the output row, then eight exponentials.  Exact float32 arithmetic and
-// libm-grade expf keep the 2e-3 budget of the float32 / TF32 mode.  QPT (adjacent queries per thread) stays at 1: with
-// two, a shared-memory load feeds twice the multiply-adds, but the halved warp count cost more than that gained
-// (256 images of 65 tokens, 6 heads of 32: 1.27 ms per forward against 1.12 ms).
+// warp reads the same 16 bytes).  Keys are taken eight at a time: eight scores, one maximum update and one rescale of
+// the output row, then eight exponentials.  Exact float32 arithmetic and libm-grade expf keep the 2e-3 budget of the
+// float32 / TF32 mode.
+// KS = 1: one thread per query, nothing exchanged between threads.  KS = 4 (grids that would not fill the GPU): four
+// adjacent lanes share a query and take the keys with index = lane part (mod 4), each with its own maximum, sum and
+// output row, merged by shuffles at the end; tile rows are padded by 16 bytes so that the four rows read by one
+// instruction fall into different banks.  The serial chain per thread is a quarter as long and there are four times
+// the warps.  (Two queries per thread, which halves the shared-memory bytes per multiply-add, was slower: too few
+// warps at 250 registers.  256 images of 65 tokens, 6 heads of 32: 1.27 ms per forward against 1.12 ms.)
 // T_main is the number of queries the row threads take; when it is below T the last CTA of each (batch, head) column
 // handles the remaining T - T_main queries with attention_f32_tail_rows instead.
-template <int HD, bool CAUSAL>
+template <int HD, bool CAUSAL, int KS>
 __global__ void __launch_bounds__(128)
 attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict__ out, int T, int T_main, int H,
                                float inv_sqrt_hd, int round_out) {
-    constexpr int QPT = 1;
     constexpr int KT = 64;                         // keys per shared-memory tile
     constexpr int V4 = HD / 4;
-    __shared__ __align__(16) float sK[KT][HD];
-    __shared__ __align__(16) float sV[KT][HD];
+    constexpr int HDP = HD + (KS > 1 ? 4 : 0);     // padded row
+    constexpr int CH = 8 * KS;                     // keys per step of the CTA: eight for each part
+    __shared__ __align__(16) float sK[KT][HDP];
+    __shared__ __align__(16) float sV[KT][HDP];
 
     const int d = H * HD;
     const long long row_stride = 3ll * d;
     const int bh = blockIdx.y, b = bh / H, h = bh % H;
-    const int q0 = blockIdx.x * blockDim.x * QPT;
-    const int qi = q0 + threadIdx.x * QPT;           // first of this thread's queries; T_main is a multiple of QPT
+    const int qpb = blockDim.x / KS;                  // queries per CTA
+    const int q0 = blockIdx.x * qpb;
+    const int part = threadIdx.x % KS;
+    const int qi = q0 + threadIdx.x / KS;
     const bool active = qi < T_main;
     const float* qbase = qkv + (long long)b * T * row_stride + h * HD;
     const float* kbase = qbase + d;
@@ -423,22 +430,19 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
         return;
     }
 
-    float q[QPT][HD], o[QPT][HD], m[QPT], l[QPT];
+    float q[HD], o[HD];
 #pragma unroll
-    for (int j = 0; j < QPT; j++) {
-#pragma unroll
-        for (int c = 0; c < V4; c++) {
-            const float4 t = active ? *reinterpret_cast<const float4*>(qbase + (long long)(qi + j) * row_stride + 4 * c)
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-            q[j][4 * c] = t.x; q[j][4 * c + 1] = t.y; q[j][4 * c + 2] = t.z; q[j][4 * c + 3] = t.w;
-            o[j][4 * c] = 0.f; o[j][4 * c + 1] = 0.f; o[j][4 * c + 2] = 0.f; o[j][4 * c + 3] = 0.f;
-        }
-        m[j] = -INFINITY; l[j] = 0.f;
+    for (int c = 0; c < V4; c++) {
+        const float4 t = active ? *reinterpret_cast<const float4*>(qbase + (long long)qi * row_stride + 4 * c)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        q[4 * c] = t.x; q[4 * c + 1] = t.y; q[4 * c + 2] = t.z; q[4 * c + 3] = t.w;
+        o[4 * c] = 0.f; o[4 * c + 1] = 0.f; o[4 * c + 2] = 0.f; o[4 * c + 3] = 0.f;
     }
-    const int kv_end = CAUSAL ? min(T, q0 + (int)blockDim.x * QPT) : T;
+    float m = -INFINITY, l = 0.f;
+    const int kv_end = CAUSAL ? min(T, q0 + qpb) : T;
     for (int k0 = 0; k0 < kv_end; k0 += KT) {
         __syncthreads();
-        const int tile_rows = min(KT, (kv_end - k0 + 7) & ~7);        // whole chunks of eight keys; rows past T are zeros
+        const int tile_rows = min(KT, (kv_end - k0 + CH - 1) / CH * CH);   // whole steps; rows past T are zeros
         for (int i = threadIdx.x; i < tile_rows * V4; i += blockDim.x) {
             const int r = i / V4, c = i % V4;
             const bool ok = k0 + r < T;
@@ -451,83 +455,71 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
         __syncthreads();
         if (!active) continue;
         const int nk = min(KT, kv_end - k0);
-        for (int c0 = 0; c0 < nk; c0 += 8) {
-            if (CAUSAL && k0 + c0 > qi + QPT - 1) break;           // every later key is masked for these queries
-            const int cw = nk - c0;                                 // live keys of this chunk (uniform over the CTA)
-            float sc[QPT][8];
+        for (int c0 = 0; c0 < nk; c0 += CH) {
+            if (CAUSAL && k0 + c0 > qi) break;                     // every later key is masked for this query
+            const int cw = KS == 1 ? nk - c0 : 8;                   // live keys of this step (uniform over the CTA)
+            float sc[8];
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
-                if (kk >= cw) {
-#pragma unroll
-                    for (int j = 0; j < QPT; j++) sc[j][kk] = -INFINITY;
-                    continue;
-                }
-                float a[QPT][4];
-#pragma unroll
-                for (int j = 0; j < QPT; j++) { a[j][0] = 0.f; a[j][1] = 0.f; a[j][2] = 0.f; a[j][3] = 0.f; }
+                if (kk >= cw) { sc[kk] = -INFINITY; continue; }
+                const int r = c0 + kk * KS + part;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int c = 0; c < V4; c++) {
-                    const float4 kv = *reinterpret_cast<const float4*>(&sK[c0 + kk][4 * c]);
-#pragma unroll
-                    for (int j = 0; j < QPT; j++) {
-                        a[j][0] = fmaf(q[j][4 * c], kv.x, a[j][0]); a[j][1] = fmaf(q[j][4 * c + 1], kv.y, a[j][1]);
-                        a[j][2] = fmaf(q[j][4 * c + 2], kv.z, a[j][2]); a[j][3] = fmaf(q[j][4 * c + 3], kv.w, a[j][3]);
-                    }
+                    const float4 kv = *reinterpret_cast<const float4*>(&sK[r][4 * c]);
+                    a0 = fmaf(q[4 * c], kv.x, a0); a1 = fmaf(q[4 * c + 1], kv.y, a1);
+                    a2 = fmaf(q[4 * c + 2], kv.z, a2); a3 = fmaf(q[4 * c + 3], kv.w, a3);
                 }
-                const int key = k0 + c0 + kk;
-#pragma unroll
-                for (int j = 0; j < QPT; j++) {
-                    const bool live = key < T && (!CAUSAL || key <= qi + j);
-                    sc[j][kk] = live ? ((a[j][0] + a[j][1]) + (a[j][2] + a[j][3])) * inv_sqrt_hd : -INFINITY;
-                }
+                const int key = k0 + r;
+                const bool live = key < T && (!CAUSAL || key <= qi);
+                sc[kk] = live ? ((a0 + a1) + (a2 + a3)) * inv_sqrt_hd : -INFINITY;
             }
-            float mn[QPT];
-            bool any = false;
+            const float cm = fmaxf(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])), fmaxf(fmaxf(sc[4], sc[5]), fmaxf(sc[6], sc[7])));
+            const float mn = fmaxf(m, cm);
+            if (mn == -INFINITY) continue;                          // nothing visible yet
+            const float alpha = expf(m - mn);                        // 0 while m is still -inf
+            l *= alpha;
 #pragma unroll
-            for (int j = 0; j < QPT; j++) {
-                const float cm = fmaxf(fmaxf(fmaxf(sc[j][0], sc[j][1]), fmaxf(sc[j][2], sc[j][3])),
-                                       fmaxf(fmaxf(sc[j][4], sc[j][5]), fmaxf(sc[j][6], sc[j][7])));
-                mn[j] = fmaxf(m[j], cm);
-                // while nothing is visible yet the reference point stays finite, so every weight below is exp(-inf) = 0
-                const float ref = mn[j] == -INFINITY ? 0.f : mn[j];
-                const float alpha = expf(m[j] - ref);                // 0 while m is still -inf
-                any = any || mn[j] != -INFINITY;
-                l[j] *= alpha;
-#pragma unroll
-                for (int c = 0; c < HD; c++) o[j][c] *= alpha;
-                m[j] = mn[j];
-                mn[j] = ref;
-            }
-            if (!any) continue;
+            for (int c = 0; c < HD; c++) o[c] *= alpha;
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
                 if (kk >= cw) break;
-                float p[QPT];
-#pragma unroll
-                for (int j = 0; j < QPT; j++) { p[j] = expf(sc[j][kk] - mn[j]); l[j] += p[j]; }   // 0 for masked keys
+                const int r = c0 + kk * KS + part;
+                const float p = expf(sc[kk] - mn);                   // 0 for masked keys
+                l += p;
 #pragma unroll
                 for (int c = 0; c < V4; c++) {
-                    const float4 vv = *reinterpret_cast<const float4*>(&sV[c0 + kk][4 * c]);
-#pragma unroll
-                    for (int j = 0; j < QPT; j++) {
-                        o[j][4 * c] = fmaf(p[j], vv.x, o[j][4 * c]); o[j][4 * c + 1] = fmaf(p[j], vv.y, o[j][4 * c + 1]);
-                        o[j][4 * c + 2] = fmaf(p[j], vv.z, o[j][4 * c + 2]); o[j][4 * c + 3] = fmaf(p[j], vv.w, o[j][4 * c + 3]);
-                    }
+                    const float4 vv = *reinterpret_cast<const float4*>(&sV[r][4 * c]);
+                    o[4 * c] = fmaf(p, vv.x, o[4 * c]); o[4 * c + 1] = fmaf(p, vv.y, o[4 * c + 1]);
+                    o[4 * c + 2] = fmaf(p, vv.z, o[4 * c + 2]); o[4 * c + 3] = fmaf(p, vv.w, o[4 * c + 3]);
                 }
             }
+            m = mn;
+        }
+    }
+    if (KS > 1) {
+        // merge the parts of a query (adjacent lanes); every thread of the warp takes part in the shuffles
+#pragma unroll
+        for (int s = 1; s < KS; s <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m, s);
+            const float l_o = __shfl_xor_sync(0xffffffffu, l, s);
+            const float m_n = fmaxf(m, m_o);
+            const float fa = m == -INFINITY ? 0.f : expf(m - m_n);
+            const float fb = m_o == -INFINITY ? 0.f : expf(m_o - m_n);
+            l = l * fa + l_o * fb;
+#pragma unroll
+            for (int c = 0; c < HD; c++) o[c] = o[c] * fa + __shfl_xor_sync(0xffffffffu, o[c], s) * fb;
+            m = m_n;
         }
     }
     if (active) {
+        float* op = out + ((long long)b * T + qi) * d + h * HD;
 #pragma unroll
-        for (int j = 0; j < QPT; j++) {
-            float* op = out + ((long long)b * T + qi + j) * d + h * HD;
-            const float inv_l = l[j];
-#pragma unroll
-            for (int c = 0; c < V4; c++) {
-                float4 r = make_float4(o[j][4 * c] / inv_l, o[j][4 * c + 1] / inv_l, o[j][4 * c + 2] / inv_l, o[j][4 * c + 3] / inv_l);
-                if (round_out) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
-                *reinterpret_cast<float4*>(op + 4 * c) = r;
-            }
+        for (int c = 0; c < V4; c++) {
+            if (KS > 1 && c % KS != part) continue;                 // the parts share the row's 16-byte stores
+            float4 r = make_float4(o[4 * c] / l, o[4 * c + 1] / l, o[4 * c + 2] / l, o[4 * c + 3] / l);
+            if (round_out) { r.x = round_tf32(r.x); r.y = round_tf32(r.y); r.z = round_tf32(r.z); r.w = round_tf32(r.w); }
+            *reinterpret_cast<float4*>(op + 4 * c) = r;
         }
     }
 }
@@ -562,8 +554,12 @@ int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H,
             const int rem = T % 32;
             const int T_main = (T >= 32 && rem > 0 && rem <= 4) ? T - rem : T;
             const int tail_cta = T_main < T ? 1 : 0;
-            const int threads = T_main >= 128 ? 128 : ((T_main + 31) / 32) * 32;
-            dim3 grid((T_main + threads - 1) / threads + tail_cta, B * H);
+            int threads = T_main >= 128 ? 128 : ((T_main + 31) / 32) * 32;
+            // a grid that would leave most SMs with a warp or two: four lanes per query instead
+            const bool split = (long long)((T_main + threads - 1) / threads) * B * H * (threads / 32) < 8ll * ctx->sm_count;
+            if (split) threads = 128;
+            const int qpb = split ? threads / 4 : threads;
+            dim3 grid((T_main + qpb - 1) / qpb + tail_cta, B * H);
             auto launch = [&](auto kern) -> int {
                 TL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
                 TL_LAUNCH(ctx, causal ? "attention_f32_causal" : "attention_f32_full", kern<<<grid, threads, 0, ctx->stream>>>(qkv, out, T, T_main, H, inv, round_out));
@@ -571,7 +567,8 @@ int launch_f32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int H,
             };
             // Tighter launch bounds (80 or 96 registers, so that all CTAs of the 65-token case are resident at once)
             // were slower: the few spilled values sit in the key loop.
-            return causal ? launch(attention_f32_rowthread_kernel<HD, true>) : launch(attention_f32_rowthread_kernel<HD, false>);
+            if (split) return causal ? launch(attention_f32_rowthread_kernel<HD, true, 4>) : launch(attention_f32_rowthread_kernel<HD, false, 4>);
+            return causal ? launch(attention_f32_rowthread_kernel<HD, true, 1>) : launch(attention_f32_rowthread_kernel<HD, false, 1>);
         }
     }
     if constexpr (HD < 32) {
