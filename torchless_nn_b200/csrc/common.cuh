@@ -178,7 +178,7 @@ struct tl_gemm_epilogue {
     int out_group = 0;
     int out_off = 0;
     float2* argmax_partials = nullptr;  // (M, tl_gemm_argmax_parts) of (max, index as float bits) or null
-    int accurate_math = 0;              // 1: libm-grade tanh in the activation, 0: hardware approximation
+    int accurate_math = 0;              // 1: activation to a few float32 ulp, 0: hardware tanh approximation
 };
 
 // A (M,K) and W (N,K) both with the contraction dimension contiguous, of element kind `prec`

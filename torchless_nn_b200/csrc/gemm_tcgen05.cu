@@ -64,16 +64,32 @@ __device__ __forceinline__ float tanh_fast(float x) {
     return y;
 }
 
+// x * sigmoid(2 u) = 0.5 x (1 + tanh(u)) without the cancellation of 1 + tanh(u) for negative u, given a = -2 u log2(e):
+// one ex2 (2^-22 relative), one reciprocal (1 ulp) and two more operations instead of a libm tanh.  The quotient is 0
+// where the exponential overflows, as the function itself is to float32 precision.
+__device__ __forceinline__ float x_sigmoid_exp2(float x, float a) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+    return x * r;
+}
+// tanh-GeLU of the reference, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), to a few float32 ulp
+__device__ __forceinline__ float gelu_precise(float x) {
+    return x_sigmoid_exp2(x, x * fmaf(x * x, -2.f * 0.0356774081f * 1.4426950409f, -2.f * 0.7978845608f * 1.4426950409f));
+}
+// x (1 + tanh(x / 2)) / 2 = x sigmoid(x)
+__device__ __forceinline__ float silu_precise(float x) { return x_sigmoid_exp2(x, x * -1.4426950409f); }
+
 template <bool ACCURATE>
 __device__ __forceinline__ float apply_act(int act, float v) {
     if (act == TLNN_ACT_GELU) {
+        if (ACCURATE) return gelu_precise(v);
         float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-        float t = ACCURATE ? tanhf(u) : tanh_fast(u);
-        return 0.5f * v * (1.f + t);
+        return 0.5f * v * (1.f + tanh_fast(u));
     }
     if (act == TLNN_ACT_SILU) {
-        float t = ACCURATE ? tanhf(0.5f * v) : tanh_fast(0.5f * v);
-        return v * ((1.f + t) * 0.5f);
+        if (ACCURATE) return silu_precise(v);
+        return v * ((1.f + tanh_fast(0.5f * v)) * 0.5f);
     }
     if (act == TLNN_ACT_RELU) return fmaxf(v, 0.f);
     return v;
@@ -86,11 +102,7 @@ __device__ __forceinline__ void apply_act_chunk(int act, float (&v)[32]) {
     if (act == TLNN_ACT_GELU) {
         if (ACCURATE) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float x = v[j];
-                const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-                v[j] = 0.5f * x * (1.f + tanhf(u));
-            }
+            for (int j = 0; j < 32; j++) v[j] = gelu_precise(v[j]);
         } else {
             // 0.5 x (1 + tanh(x (c0 + c1 x^2))) on pairs of float32 (mul / fma .f32x2): five packed instructions and
             // two hardware tanh per pair
@@ -118,8 +130,7 @@ __device__ __forceinline__ void apply_act_chunk(int act, float (&v)[32]) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
             const float x = v[j];
-            const float t = ACCURATE ? tanhf(0.5f * x) : tanh_fast(0.5f * x);
-            v[j] = x * ((1.f + t) * 0.5f);
+            v[j] = ACCURATE ? silu_precise(x) : x * ((1.f + tanh_fast(0.5f * x)) * 0.5f);
         }
     } else if (act == TLNN_ACT_RELU) {
 #pragma unroll
