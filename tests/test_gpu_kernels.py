@@ -87,6 +87,31 @@ def test_linear_in_place_residual(engine, M, K, N):
         engine.set_precision("tf32")
 
 
+@pytest.mark.parametrize("M,K,N,prec", [(16640, 192, 192, "tf32"), (16000, 96, 200, "tf32"), (16640, 192, 192, "bf16")])
+def test_linear_one_round_of_wide_tiles(engine, M, K, N, prec):
+    """130 row blocks and 129 to 256 columns: one round of 256-wide tiles on most SMs is chosen over two rounds of
+    128-wide ones.  Bias and residual through the C ABI, against NumPy."""
+    from torchless_nn_b200 import _lib, backend
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.device_array import DeviceArray
+    from torchless_nn_b200.utils import PreparedWeight
+    engine.set_precision(prec)
+    try:
+        rng = np.random.default_rng(M + K + N)
+        w = (rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)).astype(np.float32)
+        b = rng.standard_normal(N, dtype=np.float32)
+        a = rng.standard_normal((M, K), dtype=np.float32)
+        x = rng.standard_normal((M, N), dtype=np.float32)
+        wd, bd, ad, xd = (DeviceArray.from_numpy(v) for v in (w, b, a, x))
+        yd = DeviceArray.from_numpy(np.zeros((M, N), dtype=np.float32))
+        pw = PreparedWeight(wd, transpose=True)
+        check(lib.tlnn_linear_fwd(backend.ctx(), backend.precision_code(), ad.ptr, K, pw.ptr(), bd.ptr, _lib.ACT_NONE,
+                                  xd.ptr, N, yd.ptr, N, M, N, K))
+        assert rel_err(yd.get(), x + a @ w + b) < TOL[prec]
+    finally:
+        engine.set_precision("tf32")
+
+
 def test_suite_with_pair_kernel_forced():
     """TLNN_GEMM_PAIR=force routes every bf16 product through the CTA-pair kernel: the layer tests must still pass."""
     import os

@@ -717,8 +717,12 @@ int pick_bn(int M, int N, int sm_count) {
     }
     if (forced) return forced;
     const int m_tiles = (M + BM - 1) / BM;
-    if (N > 128 && (long long)m_tiles * ((N + 255) / 256) >= sm_count) return 256;
-    if (N > 64 && (long long)m_tiles * ((N + 127) / 128) >= sm_count) return 128;
+    const long long t256 = (long long)m_tiles * ((N + 255) / 256), t128 = (long long)m_tiles * ((N + 127) / 128);
+    if (N > 128 && t256 >= sm_count) return 256;
+    // one round of 256-wide tiles on most of the SMs against two rounds of 128-wide ones (16640 x 192 outputs: 130
+    // tiles against 260; 2.5 % of a whole ViT forward)
+    if (N > 128 && t256 * 4 >= sm_count * 3ll && t128 > sm_count) return 256;
+    if (N > 64 && t128 >= sm_count) return 128;
     // too few tiles to fill the SMs either way: the narrowest tile gives the most CTAs streaming the weight
     return 64;
 }
