@@ -8,8 +8,10 @@
 //  * bf16 path: flash-style kernel, 128 queries x 64 keys per step, 8 warps, operands staged with cp.async into
 //    XOR-swizzled shared memory, ldmatrix + mma.sync m16n8k16 (bf16 in, float32 accumulate), online softmax in
 //    registers with quad shuffles, exp2 with the 1/sqrt(hd) scale folded in.
-//  * float32 path: CUDA-core kernel in exact float32 arithmetic (one warp per query, keys across lanes) for the
-//    FP32/TF32 mode, where the shapes are small (T <= 128, hd 32) and operand rounding would eat the tolerance.
+//  * float32 path: CUDA-core kernels in exact float32 arithmetic for the FP32/TF32 mode, where the shapes are small
+//    (T <= 128 or a ViT's 65 / 257 tokens, hd 32) and operand rounding would eat the tolerance: head dimensions up to
+//    64 keep each query in the registers of one thread (or of four lanes when the grid is small), 96 and 128 use one
+//    warp per query with the keys across lanes.
 #include "common.cuh"
 #include <cstdlib>
 
