@@ -372,7 +372,7 @@ __device__ __forceinline__ void attention_f32_tail_rows(const float* __restrict_
         float l = 0.f, o0 = 0.f, o1 = 0.f;                 // output columns lane and lane + 32
         for (int k0 = 0; k0 < nkeys; k0 += 32) {
             const int key = k0 + lane;
-            const float p = key < nkeys ? expf(score(key) - mx) : 0.f;
+            const float p = key < nkeys ? __expf(score(key) - mx) : 0.f;
             l += p;
             const int cnt = min(32, nkeys - k0);
 #pragma unroll 8
@@ -394,7 +394,8 @@ __device__ __forceinline__ void attention_f32_tail_rows(const float* __restrict_
 // Float32 attention with the queries in registers (head dimension 8 to 64): a thread owns a query, its running
 // maximum, row sum and output row; key and value rows are read from shared memory as broadcasts (every thread of a
 // warp reads the same 16 bytes).  Keys are taken eight at a time: eight scores, one maximum update and one rescale of
-// the output row, then eight exponentials.  Exact float32 arithmetic and libm-grade expf keep the 2e-3 budget of the
+// the output row, then eight exponentials.  Exact float32 products and sums; the exponentials are ex2.approx of
+// the argument times log2(e) (2 ulp, against a dozen instructions for libm's), far inside the 2e-3 budget of the
 // float32 / TF32 mode.
 // KS = 1: one thread per query, nothing exchanged between threads.  KS = 4 (grids that would not fill the GPU): four
 // adjacent lanes share a query and take the keys with index = lane part (mod 4), each with its own maximum, sum and
@@ -479,7 +480,7 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
             const float cm = fmaxf(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])), fmaxf(fmaxf(sc[4], sc[5]), fmaxf(sc[6], sc[7])));
             const float mn = fmaxf(m, cm);
             if (mn == -INFINITY) continue;                          // nothing visible yet
-            const float alpha = expf(m - mn);                        // 0 while m is still -inf
+            const float alpha = __expf(m - mn);                        // 0 while m is still -inf
             l *= alpha;
 #pragma unroll
             for (int c = 0; c < HD; c++) o[c] *= alpha;
@@ -487,7 +488,7 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
             for (int kk = 0; kk < 8; kk++) {
                 if (kk >= cw) break;
                 const int r = c0 + kk * KS + part;
-                const float p = expf(sc[kk] - mn);                   // 0 for masked keys
+                const float p = __expf(sc[kk] - mn);                   // 0 for masked keys
                 l += p;
 #pragma unroll
                 for (int c = 0; c < V4; c++) {
@@ -506,8 +507,8 @@ attention_f32_rowthread_kernel(const float* __restrict__ qkv, float* __restrict_
             const float m_o = __shfl_xor_sync(0xffffffffu, m, s);
             const float l_o = __shfl_xor_sync(0xffffffffu, l, s);
             const float m_n = fmaxf(m, m_o);
-            const float fa = m == -INFINITY ? 0.f : expf(m - m_n);
-            const float fb = m_o == -INFINITY ? 0.f : expf(m_o - m_n);
+            const float fa = m == -INFINITY ? 0.f : __expf(m - m_n);
+            const float fb = m_o == -INFINITY ? 0.f : __expf(m_o - m_n);
             l = l * fa + l_o * fb;
 #pragma unroll
             for (int c = 0; c < HD; c++) o[c] = o[c] * fa + __shfl_xor_sync(0xffffffffu, o[c], s) * fb;
