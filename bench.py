@@ -6,16 +6,21 @@
 One "step" is one prefill of the whole workload: the GPT-2-medium-shape configuration (vocab 50257, context 2048,
 width 1024, 16 heads, 24 layers, bf16 weights with float32 accumulation) on a global batch of 64 sequences of 2048
 Zipf-distributed token ids, producing the arg-max token of every position.  The batch is sharded by rows over the
-N ranks (one process per GPU, launched by torch.distributed.run for N > 1); the only collective is an all-gather
-of the int32 tokens.  Total work is fixed as N grows ("scaling": "strong").
+N ranks (one process per GPU, started by any launcher that sets RANK / WORLD_SIZE / LOCAL_RANK, e.g.
+torch.distributed.run; this script does not import torch); the only collective is an NCCL all-gather of the int32
+tokens, issued by the library on the engine's stream.  Total work is fixed as N grows ("scaling": "strong").
 
 Printed by rank 0 as one JSON line:
   value      tokens/s with the token ids already resident in device memory (CUDA events on the engine's stream,
              maximum over ranks);
   e2e        the same metric through the public API (Network.predict_tokens) with host buffers: pinned host ids
              copied to the device and the tokens copied back inside the timed region, every step;
-  roofline   tensor-core GEMM class: algorithmic FLOPs of its launches / their summed CUDA-event durations measured
-             inside the timed region, against the measured cuBLAS bf16 rate in MEASURED_PEAKS.json;
+  roofline   tensor-core GEMM class: algorithmic FLOPs of a step's GEMM launches / their summed CUDA-event durations,
+             against the measured cuBLAS bf16 rate in MEASURED_PEAKS.json.  The per-launch events are taken in a second,
+             untimed pass: bracketing every launch serialises them and switches the captured-graph replay off, so the
+             timed region runs without them;
+  parity     the gathered tokens of the fixture's global rows against the reference's arg-max under the tie rule;
+  decode     greedy decode tokens/s of the c4 configuration (64/N prompts and their KV cache per GPU);
   cpu_baseline  the NumPy restatement of the reference's forward, timed on the host cores on a bounded sample.
 
 `--impl reference` times that CPU restatement alone (rank 0 only), one bounded sample per step.
@@ -42,12 +47,6 @@ from torchless_nn_b200 import workloads as wl  # noqa: E402
 METRIC = "gpt_prefill_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMM launches of one block, from the ncu capture summarised
-# in profiles/gemm_tcgen05_c3_prefill.md (c3: 16384 rows, width 768): 411.7 MB.  Traffic grows with rows x width, so a
-# workload's mean launch is estimated as that figure scaled by (rows x width) / (16384 x 768), times layers, plus the
-# head's operand and arg-max candidate bytes, over the number of GEMM launches.
-GEMM_BLOCK_TRAFFIC_C3 = 374.8e6
-
 
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -138,14 +137,18 @@ def cpu_sample(spec, params, ids_row, block_index: int):
 
 
 def cpu_threads() -> int:
+    """Give the BLAS behind NumPy every core this process may run on, and say how many that is.  A launcher that
+    exports OMP_NUM_THREADS=1 to its workers (torch.distributed.run does) would otherwise halve the baseline."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
-        from threadpoolctl import threadpool_info
-        n = [i.get("num_threads", 0) for i in threadpool_info() if i.get("user_api") == "blas"]
-        if n:
-            return int(max(n))
+        from threadpoolctl import threadpool_info, threadpool_limits
+        threadpool_limits(limits=n, user_api="blas")        # stays in force: the returned object is not used as a context
+        got = [i.get("num_threads", 0) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if got:
+            return int(max(got))
     except Exception:
         pass
-    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return n
 
 
 def cpu_tokens_per_s(spec, params, ids, n_samples: int):
@@ -161,19 +164,29 @@ CPU_SAMPLE_TEXT = ("one of the {B} sequences at the full {T}-token context throu
                    "timed; sequence time = embed + {L} x block + tail")
 
 
-def config_dict(spec, n_gpus):
+def dtype_of(spec) -> str:
+    """Arithmetic type of the path for this configuration: bf16 operands (float32 accumulation) or TF32."""
+    return "bf16" if spec.precision == "bf16" else "tf32"
+
+
+def config_dict(spec, n_gpus, batch=None):
+    head = "tied head (token table)" if spec.tied_head else "untied Dense head"
+    arith = "bf16 weights / fp32 accumulate" if spec.precision == "bf16" else "fp32 storage, TF32 tensor-core operands"
+    dist = "Zipf(1.1)" if spec.input_dist == "zipf" else "uniform"
     return {"workload": f"{spec.name}: GPT prefill, vocab {spec.vocab}, context {spec.context}, d_model {spec.d_model}, "
-                        f"{spec.heads} heads, {spec.layers} layers, FFN {4 * spec.d_model} GeLU-tanh, tied head, "
-                        f"bf16 weights / fp32 accumulate, arg-max token per position",
-            "global_batch": spec.batch, "seq_len": spec.seq_len, "parallelism": f"batch-sharded x{n_gpus}",
-            "weights": "N(0,0.02) seed 0", "inputs": f"Zipf(1.1) token ids seed {spec.input_seed}",
-            "l2": "no flush needed: 0.7 GB of bf16 weights and several GB of activations per step exceed the 126 MB L2"}
+                        f"{spec.heads} heads, {spec.layers} layers, FFN {4 * spec.d_model} GeLU-tanh, {head}, "
+                        f"{arith}, arg-max token per position",
+            "global_batch": batch or spec.batch, "seq_len": spec.seq_len, "parallelism": f"batch-sharded x{n_gpus}",
+            "weights": "N(0,0.02) seed 0", "inputs": f"{dist} token ids seed {spec.input_seed}",
+            "l2": "no flush: the step streams its weights and several GB of activations, far more than the 126 MB L2"
+                  if spec.d_model >= 768 else "no flush: the step is launch-bound, its working set is a few MB"}
 
 
 def run_reference(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    cores = cpu_threads()
     params = wl.seeded_params(spec)
     ids = wl.make_inputs(spec, 4)
     for i in range(args.warmup):
@@ -186,7 +199,6 @@ def run_reference(args, spec):
         rates.append(spec.seq_len / (e + spec.layers * b + t))
     wall = time.perf_counter() - t_all
     value = statistics.median(rates)
-    cores = cpu_threads()
     sample = CPU_SAMPLE_TEXT.format(B=spec.batch, T=spec.seq_len, L=spec.layers)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * wall / max(args.steps, 1), "higher_is_better": True,
@@ -201,14 +213,54 @@ def run_reference(args, spec):
     return 0
 
 
-def run_b200(args, spec):
-    import ctypes as C
-    from torchless_nn_b200 import backend, _lib
-    from torchless_nn_b200._lib import lib, check
-    from torchless_nn_b200.device_array import DeviceArray
-    from torchless_nn_b200.models import build_network, load_params
-    from torchless_nn_b200.network import GPTPlan
+# ------------------------------------------------------------------------------------------------ golden checks
+def golden_rows_match(name: str, tokens: np.ndarray, tol_rel: float):
+    """Compare rows of a gathered (B, T) token array with the fixture the reference wrote for this configuration
+    (tests/golden/<name>.npz: arg-max, top and runner-up logit of whole sequences, stored with their global row
+    numbers).  Tokens must be identical except where the reference's own top-2 gap is below the tolerance.
+    Returns (all rows pass, rows checked, differing tokens, unexcused differences); (None, 0, 0, 0) without a fixture."""
+    path = os.path.join(ROOT, "tests", "golden", name + ".npz")
+    if not os.path.exists(path):
+        return None, 0, 0, 0
+    g = np.load(path)
+    rows = g["global_rows"] if "global_rows" in g.files else np.arange(int(g["n_seq"]))
+    ok, n_diff, n_bad, checked = True, 0, 0, 0
+    for s, r in enumerate(rows):
+        if r >= tokens.shape[0]:
+            continue
+        p = f"seq{s}_"
+        tol = tol_rel * float(g[p + "max_abs"])
+        T = min(tokens.shape[1], g[p + "argmax"].shape[0])
+        differ = tokens[r, :T] != g[p + "argmax"][:T]
+        excused = (g[p + "top"][:T] - g[p + "second"][:T]) < tol
+        n_diff += int(differ.sum())
+        n_bad += int((differ & ~excused).sum())
+        checked += 1
+    return bool(n_bad == 0 and checked > 0), checked, n_diff, n_bad
 
+
+def decode_rows_match(tokens: np.ndarray, n_prompt: int, tol_rel: float):
+    """Gathered greedy continuations against the reference's literal recompute loop (tests/golden/c4.npz: the first
+    prompts, a few dozen steps): equal until the first step at which the reference's own top-2 gap is below the
+    tolerance (after a near-tie the two sequences may legitimately go different ways)."""
+    path = os.path.join(ROOT, "tests", "golden", "c4.npz")
+    if not os.path.exists(path):
+        return None
+    g = np.load(path)
+    tol = tol_rel * float(g["max_abs"])
+    for b in range(min(int(g["n_prompts"]), tokens.shape[0])):
+        for t in range(min(int(g["steps"]), tokens.shape[1] - n_prompt)):
+            if tokens[b, n_prompt + t] != g["tokens"][b, n_prompt + t]:
+                if g["top"][b, t] - g["second"][b, t] >= tol:
+                    return False
+                break
+    return True
+
+
+# ------------------------------------------------------------------------------------------------ the engine arm
+def open_ranks(args):
+    """Rank, world and (for N > 1) the NCCL communicator of this process.  One process per GPU; the launcher
+    (torch.distributed.run or any other) only sets RANK / WORLD_SIZE / LOCAL_RANK."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -218,168 +270,279 @@ def run_b200(args, spec):
                              "--nproc-per-node N bench.py --gpus N ...`")
         raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE={world}")
     os.environ["TLNN_DEVICE"] = str(local_rank)
-
-    dist = None
-    torch = None
+    comm = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from torchless_nn_b200.comm import Communicator
+        comm = Communicator.from_env()
+    return rank, world, local_rank, comm
 
+
+class Timer:
+    """CUDA events on the engine's stream around a region, bracketed by a barrier over the ranks and a stream
+    synchronise on both sides; the reported time is the maximum over ranks."""
+
+    def __init__(self, ctx, comm):
+        self.ctx, self.comm = ctx, comm
+
+    def barrier(self):
+        from torchless_nn_b200 import backend
+        backend.synchronize()
+        if self.comm:
+            self.comm.barrier()
+
+    def run(self, fn, steps: int) -> float:
+        import ctypes as C
+        from torchless_nn_b200._lib import lib, check
+        ms = C.c_float()
+        self.barrier()
+        check(lib.tlnn_prof_begin(self.ctx))
+        for _ in range(steps):
+            fn()
+        check(lib.tlnn_prof_end(self.ctx, C.byref(ms)))
+        self.barrier()
+        return self.comm.max_over_ranks(float(ms.value)) if self.comm else float(ms.value)
+
+
+def class_table(ctx, fn, repeats: int = 1):
+    """Per-kernel-class CUDA-event times of `repeats` runs of fn, in an untimed pass of its own: bracketing every
+    launch with events serialises the launches and switches graph replay off, so it must not run inside a timed
+    region.  Returns {class: (launches, ms)} per run."""
+    from torchless_nn_b200 import _lib
+    from torchless_nn_b200._lib import lib, check
+    check(lib.tlnn_prof_classes(ctx, 1))
+    for _ in range(repeats):
+        fn()
+    rows = (_lib.ProfRow * 96)()
+    n_rows = lib.tlnn_prof_table(ctx, rows, 96)
+    check(lib.tlnn_prof_classes(ctx, 0))
+    return {r.name.decode(): (int(r.launches) / repeats, float(r.ms) / repeats) for r in rows[:n_rows]}
+
+
+# DRAM traffic of the four weight GEMMs of one c5 block on an 8-sequence shard (16384 rows, width 1024), from an ncu
+# capture of exactly that case (dram__bytes_read.sum + dram__bytes_write.sum summed over the four launches).  Every
+# operand and output of these products is streamed once, so traffic grows in proportion to the rows; the weights
+# (25 MB per block) are the part that does not, and they are 2 % of the figure.
+GEMM_BLOCK_TRAFFIC = {"rows": 16384, "d_model": 1024, "bytes": None}
+
+
+def measure_decode(args, rank, world, comm, timer):
+    """Greedy decode on the GPT-2-small-shape model (the c4 configuration): 64 prompts of 128 tokens shared out by
+    rows, every rank keeps the KV cache of its own prompts, 256 new tokens each, one gather of the finished rows."""
+    from torchless_nn_b200 import backend
+    from torchless_nn_b200.models import build_seeded
+    spec = wl.CONFIGS["c4"]
+    spec, net = build_seeded(spec)
+    prompts = wl.make_inputs(spec)
+    new = args.new_tokens
+    out = {}
+
+    def step():
+        out["tokens"] = net.generate_greedy(prompts, new, comm=comm)
+
+    for _ in range(2):
+        step()
+    backend.launch_count(reset=True)
+    ms = timer.run(step, args.decode_runs) / args.decode_runs
+    launches = backend.launch_count() / args.decode_runs
+    tokens = out["tokens"].get()
+    lo, hi = wl.shard_rows(spec.batch, rank, world)
+    d, L = spec.d_model, spec.layers
+    w_bytes = 2.0 * (spec.n_params() - spec.context * d)                  # bf16; the tied table doubles as the head
+    kv_bytes = sum(2.0 * (hi - lo) * L * (spec.seq_len + i) * d * 2 for i in range(new))
+    hbm = (w_bytes * new + kv_bytes) / (ms * 1e-3) / 1e9
+    peak_hbm = measured_hbm()
+    res = {"metric": "gpt_greedy_decode_new_tokens_per_s", "value": spec.batch * new / (ms * 1e-3), "unit": UNIT,
+           "workload": f"c4: {spec.batch} prompts x {spec.seq_len} tokens + {new} greedy tokens on the c3-shape model, "
+                       f"{spec.batch}/{world} prompts and their KV cache per GPU, prompt prefill inside the timed run",
+           "ms_per_run": ms, "ms_per_step": ms / new, "launches_per_run": launches,
+           "hbm_gbs_per_gpu": hbm, "hbm_peak_gbs": peak_hbm, "frac_of_measured_hbm": hbm / peak_hbm,
+           "algorithmic_bytes_per_gpu_per_run": w_bytes * new + kv_bytes,
+           "tokens_match_golden": decode_rows_match(tokens, spec.seq_len, 3e-2) if rank == 0 else None}
+    backend.set_precision(wl.CONFIGS[args.config].precision)
+    return res
+
+
+def measured_hbm():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def run_b200(args, spec):
+    import ctypes as C
+    from torchless_nn_b200 import backend, _lib
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.device_array import DeviceArray
+    from torchless_nn_b200.models import build_network, load_params
+    from torchless_nn_b200.network import GPTPlan
+
+    rank, world, local_rank, comm = open_ranks(args)
     backend.set_precision(spec.precision)
     ctx = backend.ctx()
+    timer = Timer(ctx, comm)
     net = build_network(spec)
     load_params(net, wl.seeded_params(spec))
-    ids_all = wl.make_inputs(spec)
-    lo, hi = wl.shard_rows(spec.batch, rank, world)
+    batch = args.batch or spec.batch
+    ids_all = wl.make_inputs(spec, batch)
+    lo, hi = wl.shard_rows(batch, rank, world)
     ids_local = np.ascontiguousarray(ids_all[lo:hi])
     B_local, T = ids_local.shape
     n_local = B_local * T
-    n_global = spec.batch * T
+    n_global = batch * T
+    tol_rel = 3e-2 if spec.precision == "bf16" else 2e-3
 
     plan = GPTPlan.match(net.layers)
     model, keep, V = plan.model()
     ids_dev = DeviceArray.from_numpy(ids_local)
     tok_local = DeviceArray((B_local, T), np.int32)
-    tok_all = DeviceArray((spec.batch, T), np.int32) if world > 1 else tok_local
+    tok_all = DeviceArray((batch, T), np.int32) if comm else tok_local
+    counts = None
+    if comm:
+        from torchless_nn_b200.comm import shard_counts
+        counts = (C.c_longlong * world)(*[r * T for r in shard_counts(batch, world)])
 
-    gather = None
-    if world > 1:
-        if spec.batch % world != 0:
-            raise SystemExit("the global batch must divide evenly over the ranks for the token all-gather")
-        ext = torch.cuda.ExternalStream(int(lib.tlnn_stream(ctx)), device=torch.device("cuda", local_rank))
-        t_local = torch.as_tensor(tok_local, device=torch.device("cuda", local_rank))
-        t_all = torch.as_tensor(tok_all, device=torch.device("cuda", local_rank))
-
-        def gather():
-            # NCCL orders the collective after the work already enqueued on the engine's stream
-            with torch.cuda.stream(ext):
-                dist.all_gather_into_tensor(t_all.view(-1), t_local.view(-1))
+    def prefill():
+        check(lib.tlnn_gpt_prefill(ctx, C.byref(model), ids_dev.ptr, _lib.I32, B_local, T, None, tok_local.ptr))
 
     def step_resident():
-        check(lib.tlnn_gpt_prefill(ctx, C.byref(model), ids_dev.ptr, _lib.I32, B_local, T, None, tok_local.ptr))
-        if gather:
-            gather()
+        prefill()
+        if comm:
+            check(lib.tlnn_allgather_tokens(comm._h, tok_local.ptr, tok_all.ptr, n_local, counts))
 
-    def barrier():
-        backend.synchronize()
-        if dist:
-            dist.barrier()
-        backend.synchronize()
-
-    def max_over_ranks(ms: float) -> float:
-        if not dist:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-resident throughput ---------------------------------------------------------------------------
+    # ---- device-resident throughput: the default product path (captured graph replay, no per-launch events) ---------
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step_resident()
-    barrier()
-    check(lib.tlnn_prof_classes(ctx, 1))
+    timer.barrier()
     backend.launch_count(reset=True)
-    ms = C.c_float()
-    barrier()
     sampler.mark()                     # clocks are counted from here to the end of the timed region
-    check(lib.tlnn_prof_begin(ctx))
-    for _ in range(args.steps):
-        step_resident()
-    check(lib.tlnn_prof_end(ctx, C.byref(ms)))
-    barrier()
+    total_ms = timer.run(step_resident, args.steps)
     launches = backend.launch_count()
     clocks = sampler.stop() if rank == 0 else None
-    rows = (_lib.ProfRow * 64)()
-    n_rows = lib.tlnn_prof_table(ctx, rows, 64)
-    check(lib.tlnn_prof_classes(ctx, 0))
-    total_ms = max_over_ranks(float(ms.value))
     value = n_global * args.steps / (total_ms * 1e-3)
-    classes = {r.name.decode(): (int(r.launches), float(r.ms)) for r in rows[:n_rows]}
+    resident_tokens = tok_all.get() if rank == 0 else None
+    match_resident = golden_rows_match(spec.name, resident_tokens, tol_rel) if rank == 0 else None
+
+    # ---- per-class breakdown and the GEMM roofline: a separate, untimed pass ---------------------------------------
+    classes = class_table(ctx, prefill, repeats=2)
+    class_ms = sum(v[1] for v in classes.values())
     gemm_ms = sum(v[1] for k, v in classes.items() if k.startswith("gemm_"))
     gemm_launches = sum(v[0] for k, v in classes.items() if k.startswith("gemm_"))
     d, L = spec.d_model, spec.layers
-    gemm_flops = args.steps * n_local * (L * 24.0 * d * d + 2.0 * d * spec.vocab)
+    gemm_flops = n_local * (L * 24.0 * d * d + 2.0 * d * spec.vocab)
     peak, peak_how = measured_peak()
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel / gemm_tcgen05_kernel (all GEMM launches)", "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_how,
-                "traffic": ((GEMM_BLOCK_TRAFFIC_C3 * (n_local * d) / (16384.0 * 768.0)) * L
-                            + n_local * d * 2.0 + spec.vocab * d * 2.0 + n_local * 394 * 8.0) / (4 * L + 1),
-                "traffic_note": "mean DRAM bytes per GEMM launch, scaled from the c3 ncu capture by rows x width",
+    step_ms_rank = total_ms / args.steps
+    traffic = None
+    if GEMM_BLOCK_TRAFFIC["bytes"] and d == GEMM_BLOCK_TRAFFIC["d_model"]:
+        # mean over the 4 L block products (the head product is not part of the capture)
+        traffic = GEMM_BLOCK_TRAFFIC["bytes"] * (n_local / GEMM_BLOCK_TRAFFIC["rows"]) / 4.0
+    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel / gemm_tcgen05_kernel (all GEMM launches of a step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_how,
+                "traffic": traffic,
+                "traffic_note": "mean DRAM bytes per block GEMM launch: ncu capture of one block's four products at 16384 rows x "
+                                "1024, scaled by this rank's rows" if traffic else None,
                 "algorithmic_bytes_per_launch": (n_local * (d * 2.0 * 7 + d * 4.0 * 4 + 3 * d * 2.0 + 4 * d * 2.0) * L
-                                                 + 12.0 * d * d * 2 * L + n_local * d * 2.0 + spec.vocab * d * 2.0) / (4 * L + 1),
-                "launches": gemm_launches,
-                "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                "share_of_step": gemm_ms / float(ms.value) if ms.value else None,
-                "kernel_classes_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(classes.items())},
-                "whole_step_tflops_per_gpu": spec.flops_per_token() * n_local * args.steps / (float(ms.value) * 1e-3) / 1e12,
+                                                 + 12.0 * d * d * 2 * L) / (4 * L),
+                "launches_per_step": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
+                "measured": "CUDA events around every launch, in an untimed pass after the timed region (the events "
+                            "serialise launches, so they are kept out of it)",
+                "share_of_step": gemm_ms / class_ms if class_ms else None,
+                "kernel_classes_ms_per_step": {k: round(v[1], 4) for k, v in sorted(classes.items())},
+                "whole_step_tflops_per_gpu": spec.flops_per_token() * n_local / (step_ms_rank * 1e-3) / 1e12,
                 "frac_of_nominal_2250": achieved / 2250.0}
 
     # ---- end to end through the public API, host buffers -----------------------------------------------------------
     hp = C.c_void_p()
-    check(lib.tlnn_host_alloc(ids_local.nbytes, C.byref(hp)))
-    pinned_ids = np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_int32)), shape=ids_local.shape)
-    pinned_ids[...] = ids_local
-    out_rows = spec.batch if (world > 1 and rank == 0) else B_local
+    check(lib.tlnn_host_alloc(ids_all.nbytes, C.byref(hp)))
+    pinned_ids = np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_int32)), shape=ids_all.shape)
+    pinned_ids[...] = ids_all
+    out_rows = batch if rank == 0 else B_local
     hq = C.c_void_p()
     check(lib.tlnn_host_alloc(out_rows * T * 4, C.byref(hq)))
     pinned_tok = np.ctypeslib.as_array(C.cast(hq, C.POINTER(C.c_int32)), shape=(out_rows, T))
 
     def step_e2e():
-        dev_ids = DeviceArray(ids_local.shape, np.int32)
-        check(lib.tlnn_h2d(ctx, dev_ids.ptr, pinned_ids.ctypes.data, pinned_ids.nbytes))
-        tok = net.predict_tokens(dev_ids)
-        src = tok
-        if gather:
-            check(lib.tlnn_d2d(ctx, tok_local.ptr, tok.ptr, tok.nbytes))
-            gather()
-            src = tok_all if rank == 0 else tok_local
+        # the call a user makes: the global batch in host memory, every rank uploads and runs its rows, tokens gathered
+        tok = net.predict_tokens(pinned_ids, comm=comm)
+        src = tok if rank == 0 else DeviceArray((B_local, T), np.int32, ptr=tok.ptr + lo * T * 4, root=tok)
         check(lib.tlnn_d2h(ctx, pinned_tok.ctypes.data, src.ptr, pinned_tok.nbytes))
-        return pinned_tok
 
     for _ in range(2):
         step_e2e()
-    barrier()
-    check(lib.tlnn_prof_begin(ctx))
-    for _ in range(args.steps):
-        step_e2e()
-    ms2 = C.c_float()
-    check(lib.tlnn_prof_end(ctx, C.byref(ms2)))
-    barrier()
-    e2e_ms = max_over_ranks(float(ms2.value))
+    e2e_ms = timer.run(step_e2e, args.steps)
     e2e_value = n_global * args.steps / (e2e_ms * 1e-3)
-    same = bool(np.array_equal(pinned_tok[:B_local] if out_rows != B_local else pinned_tok, tok_local.get())) \
-        if rank == 0 and world == 1 else None
+    match_e2e = golden_rows_match(spec.name, np.array(pinned_tok), tol_rel) if rank == 0 else None
+    same = bool(np.array_equal(pinned_tok, resident_tokens)) if rank == 0 else None
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(spec, world), "clocks": clocks,
+            "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": dtype_of(spec), "data": "synthetic",
+            "config": config_dict(spec, world, batch), "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(ids_local.nbytes),
                     "d2h_bytes_per_step": int(pinned_tok.nbytes), "ms_per_step": e2e_ms / args.steps,
-                    "api": "Network.predict_tokens(pinned host ids) + token all-gather + copy to pinned host memory",
+                    "api": "Network.predict_tokens(global batch in pinned host memory, comm): upload of this rank's rows, "
+                           "prefill, NCCL all-gather of the tokens, copy to pinned host memory",
                     "tokens_equal_resident_path": same},
             "gpu_launches": int(launches), "roofline": roofline,
             "tokens_per_s_per_gpu": value / world,
             "frac_of_nominal_bf16_whole_step": roofline["whole_step_tflops_per_gpu"] / 2250.0}
+    if rank == 0:
+        ok_r, n_rows, n_diff, n_bad = match_resident
+        ok_e = match_e2e[0]
+        line["e2e"]["tokens_match_golden"] = ok_e
+        line["parity"] = {"tokens_match_golden": None if ok_r is None else bool(ok_r and ok_e),
+                          "fixture_rows_checked": n_rows, "tokens_differing": n_diff, "unexcused": n_bad,
+                          "rule": "gathered tokens of the fixture's global rows equal the reference's arg-max except "
+                                  f"where the reference's top-2 gap is below {tol_rel} x max|logit|"}
+
+    if not args.no_decode and spec.name == "c5" and not args.batch:
+        line["decode"] = measure_decode(args, rank, world, comm, timer)
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = cpu_threads()
         params = wl.seeded_params(spec)
         v = cpu_tokens_per_s(spec, params, ids_all[:2], 2)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": CPU_SAMPLE_TEXT.format(B=spec.batch, T=spec.seq_len, L=spec.layers)}
     if rank == 0:
         print(json.dumps(line), flush=True)
     lib.tlnn_host_free(hp)
     lib.tlnn_host_free(hq)
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
+    if comm:
+        comm.barrier()
+        comm.close()
+    return 0
+
+
+def run_decode(args, spec):
+    """`--config c4`: the decode measurement on its own, at any number of GPUs."""
+    from torchless_nn_b200 import backend
+    rank, world, local_rank, comm = open_ranks(args)
+    ctx = backend.ctx()
+    timer = Timer(ctx, comm)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        sampler.mark()
+    res = measure_decode(args, rank, world, comm, timer)
+    line = {"metric": res["metric"], "value": res["value"], "unit": UNIT, "n_gpus": world, "steps": args.decode_runs,
+            "warmup": 2, "ms_per_step": res["ms_per_run"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": res["workload"]},
+            "clocks": sampler.stop() if rank == 0 else None, "gpu_launches": int(res["launches_per_run"] * args.decode_runs),
+            "roofline": {"bound": "hbm", "achieved": res["hbm_gbs_per_gpu"], "peak": res["hbm_peak_gbs"], "unit": "GB/s",
+                         "frac": res["frac_of_measured_hbm"], "traffic": None},
+            "decode": res}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if comm:
+        comm.barrier()
+        comm.close()
     return 0
 
 
@@ -465,14 +628,18 @@ def main():
     ap.add_argument("--config", default="c5", choices=["c5", "c3", "c1", "c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sample", action="store_true", help="c4 only: sampled decode (the notebook's GPT.generate) instead of arg-max")
-    ap.add_argument("--batch", type=int, default=0, help="c4 --sample only: number of prompt rows (default: the config's 64)")
+    ap.add_argument("--batch", type=int, default=0, help="rows of the global batch (default: the configuration's)")
+    ap.add_argument("--no-decode", action="store_true", help="c5: skip the decode measurement added to the line")
+    ap.add_argument("--decode-runs", type=int, default=3, help="timed runs of the decode measurement")
     ap.add_argument("--new-tokens", type=int, default=wl.C4_NEW_TOKENS, help="c4 only: tokens generated per prompt")
     args = ap.parse_args()
     spec = wl.CONFIGS[args.config]
     if args.impl == "reference":
         return run_reference(args, spec)
-    if args.config in ("c2", "c4"):
+    if args.config == "c2" or (args.config == "c4" and args.sample):
         return run_other(args, spec)
+    if args.config == "c4":
+        return run_decode(args, spec)
     return run_b200(args, spec)
 
 

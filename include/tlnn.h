@@ -179,8 +179,12 @@ int tlnn_norm_logits_fwd(tlnn_ctx* ctx, int prec, const float* x, const float* g
  * latency-critical loop that cannot afford the device-wide stall an allocation may cause.
  *  - Every GPU that loads libtlnn.so keeps the array resident until the process exits.
  *  - Shapes whose intermediates exceed the array are refused with TLNN_ERR_VALUE and a message that states the need.
- *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that call during
- *    set-up, before any stream capture begins.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress), and the first call for a
+ *    given precision and shape class sets the attributes of the kernel variant it picks; make one call per precision
+ *    and shape you will use during set-up, before any stream capture begins.  The address is cached in a plain
+ *    per-device table written without a lock: two threads that race through their first call store the same value.
+ *  - Keep per-class profiling (tlnn_prof_classes) off around this call: with it on, every launch takes CUDA events
+ *    from a pool that creates new ones when it is empty.
  *  - All calls on a device share the one array and leave their data in it; nothing in it has to be zero on entry.
  *    Two calls whose kernels can overlap on the GPU (different contexts/streams on one device) race: serialise them. */
 #define TLNN_NOALLOC_SCRATCH_BYTES (16u << 20)
@@ -230,6 +234,36 @@ int tlnn_decode_first_sampled(tlnn_decoder* dec, float temperature, const double
 int tlnn_decode_run_sampled(tlnn_decoder* dec, const int32_t* prev_tokens, int n_steps, float temperature,
                             const double* uniforms, int32_t* tokens_out);
 int tlnn_decode_end(tlnn_decoder* dec);
+
+/* ---- multi-GPU: batch-sharded replicas ------------------------------------ */
+/* The reference is single-device: Network.predict (network.py:33-39) runs the whole batch in one process.  Eval-mode
+ * rows are independent (LayerNorm is per row, layers.py:419-420; attention is per sample, layers.py:293-304), so N
+ * processes, one per GPU with its own context and a full copy of the weights, each run a contiguous slice of the batch
+ * rows and exchange only results.  A communicator wraps NCCL (bound at run time: TLNN_NCCL_LIB, else libnccl.so.2;
+ * a process without NCCL can use everything else in this header).
+ *   tlnn_comm_unique_id  rank 0 creates TLNN_COMM_ID_BYTES opaque bytes and hands them to the other ranks by whatever
+ *                        means the launcher offers (a file, a socket, MPI, a key-value store).
+ *   tlnn_comm_init       every rank calls it with the same bytes, its rank and the world size; collective: returns
+ *                        once all ranks have joined.  TLNN_COMM_FAIL_INIT=1 makes it fail before any GPU or network
+ *                        work (host-side failure injection for tests).
+ *   tlnn_allgather_tokens / tlnn_allgather_logits
+ *                        `local` holds this rank's n_local results (arg-max tokens of its rows: xp.argmax,
+ *                        network.py:135,158; or logits rows), `all` receives every rank's block in rank order.  counts
+ *                        (host array of `world` entries, may be NULL when every rank passes the same n_local) allows
+ *                        ragged shards.  Enqueued on the context's compute stream, after the kernels that write
+ *                        `local`; `all` is valid after the next tlnn_sync / tlnn_d2h.
+ *   tlnn_comm_barrier    a one-int all-reduce followed by tlnn_sync: every rank has finished its enqueued work.
+ * Calls on a communicator must be made in the same order on every rank. */
+#define TLNN_COMM_ID_BYTES 128
+typedef struct tlnn_comm tlnn_comm;
+int tlnn_comm_nccl_version(int* version);
+int tlnn_comm_unique_id(void* id_bytes);
+int tlnn_comm_init(tlnn_ctx* ctx, const void* id_bytes, int rank, int world, tlnn_comm** out);
+int tlnn_comm_rank(tlnn_comm* comm, int* rank, int* world);
+int tlnn_allgather_tokens(tlnn_comm* comm, const int32_t* local, int32_t* all, long long n_local, const long long* counts);
+int tlnn_allgather_logits(tlnn_comm* comm, const float* local, float* all, long long n_local, const long long* counts);
+int tlnn_comm_barrier(tlnn_comm* comm);
+int tlnn_comm_destroy(tlnn_comm* comm);
 
 /* ---- double-buffered host feed ------------------------------------------- */
 /* The reference uploads every batch synchronously (`xp.array(batch)`, network.py:117,152).  A feeder owns two pinned

@@ -121,29 +121,34 @@ def gen_small(ref, name):
     print(name, "ref", round(dt, 2), "s  oracle diff", diff, "max|logit|", out["max_abs"])
 
 
-def gen_large(ref, name, n_seq):
+def gen_large(ref, name, rows):
+    """Whole sequences of a large configuration, one at a time (batch rows are independent).  ``rows`` are GLOBAL row
+    indices of the configuration's batch: sequence ``s`` of the fixture is global row ``rows[s]`` (stored as
+    ``global_rows``), so that every rank of a batch-sharded run owns at least one pinned sequence."""
     spec = wl.CONFIGS[name]
     params = wl.seeded_params(spec)
-    x = wl.make_inputs(spec, n_seq)
+    x = wl.make_inputs(spec)
     net = build_reference_net(ref, spec)
     load_seeded(net, params)
     out = {}
     diffs, secs = [], []
-    for s in range(n_seq):
+    for s, r in enumerate(rows):
         t0 = time.time()
-        y = net.predict(x[s:s + 1])[0]
+        y = net.predict(x[r:r + 1])[0]
         secs.append(time.time() - t0)
         if s == 0:
-            yo = onp.gpt_forward(spec, params, x[s:s + 1])[0]
+            yo = onp.gpt_forward(spec, params, x[r:r + 1])[0]
             diffs.append(float(np.abs(y - yo).max()))
         sm = summarise(y)
-        rows, cols, vals = sampled(y, seed=1000 + s)
+        pos, cols, vals = sampled(y, seed=1000 + s)
         for k, v in sm.items():
             out[f"seq{s}_{k}"] = v
-        out[f"seq{s}_rows"], out[f"seq{s}_cols"], out[f"seq{s}_vals"] = rows, cols, vals
-        out[f"seq{s}_hidden_rows"] = net.layers[-2].output[0][rows].astype(np.float32)
-        print(name, "seq", s, round(secs[-1], 1), "s", "max|logit|", sm["max_abs"], flush=True)
-    out["n_seq"] = np.int32(n_seq)
+        out[f"seq{s}_rows"], out[f"seq{s}_cols"], out[f"seq{s}_vals"] = pos, cols, vals
+        if s < 2:
+            out[f"seq{s}_hidden_rows"] = net.layers[-2].output[0][pos].astype(np.float32)
+        print(name, "seq", s, "global row", r, round(secs[-1], 1), "s", "max|logit|", sm["max_abs"], flush=True)
+    out["n_seq"] = np.int32(len(rows))
+    out["global_rows"] = np.asarray(rows, dtype=np.int32)
     out["oracle_max_abs_diff"] = np.float32(max(diffs))
     out["ref_seconds_per_seq"] = np.float32(np.mean(secs))
     np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **out)
@@ -392,9 +397,9 @@ def main():
         elif w in ("c1", "c2"):
             gen_small(ref, w)
         elif w == "c3":
-            gen_large(ref, "c3", 2)
+            gen_large(ref, "c3", [0, 1, 2, 4, 6, 8, 10, 12, 14])      # rows 0 and 1, then one per rank of an 8-way shard
         elif w == "c5":
-            gen_large(ref, "c5", 1)
+            gen_large(ref, "c5", [0, 8, 16, 24, 32, 40, 48, 56])      # one sequence per rank of an 8-way shard
         elif w == "c4":
             gen_decode(ref)
         elif w == "ckpt":

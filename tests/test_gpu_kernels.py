@@ -413,3 +413,68 @@ def test_expired_wait_is_reported_and_the_context_survives(engine):
         assert rel_err(layer.forward(x).get(), x @ w) < TOL["bf16"]
     finally:
         engine.set_precision("tf32")
+
+
+# ----------------------------------------------------------------------------- Residual wrapper, profiling, misc ABI
+def test_residual_add_around_feed_forward(engine, prec, golden):
+    """Residual(mode="add") (utils.py:76-88) on device arrays: x + feed_forward(x), against the reference's own
+    feed-forward output from the fixture."""
+    from torchless_nn_b200 import activations
+    from torchless_nn_b200.layers import TransformerFeedForward
+    from torchless_nn_b200.utils import Residual
+    g = golden("layers")
+    ff = TransformerFeedForward(96, activations.GeLU)
+    for name, p in (("w1", ff.weights1), ("b1", ff.bias1), ("w2", ff.weights2), ("b2", ff.bias2)):
+        _load(g[f"ffn_gelu_{name}"], p)
+    res = Residual([ff], mode="add")
+    res.set_eval(True)
+    x = g["ffn_gelu_x"]
+    y = res.forward(x)
+    want = x + g["ffn_gelu_y"]
+    assert y.shape == x.shape and rel_err(y.get(), want) < TOL[prec]
+    params = [g[f"ffn_gelu_{n}"] for n in ("w1", "b1", "w2", "b2")]
+    assert rel_err(y.get(), x + onp.feed_forward(x, *params, act="gelu")) < TOL[prec]
+    assert res.output is y and np.array_equal(res.input.get(), x)
+    assert len(res.parameters) == 4 and res.parameters[0] is ff.weights1
+    with pytest.raises(NotImplementedError):
+        Residual([ff], mode="concat").forward(x)
+
+
+def test_profiling_entry_points(engine):
+    """tlnn_prof_begin/end time a region with CUDA events; tlnn_prof_classes/table give per-kernel-class launches and
+    times; tlnn_device_info and tlnn_d2h_async are part of the same ABI."""
+    import ctypes as C
+    from torchless_nn_b200 import _lib, backend
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.layers import LayerNorm
+    ctx = backend.ctx()
+    sm, total, free = C.c_int(), C.c_size_t(), C.c_size_t()
+    check(lib.tlnn_device_info(ctx, C.byref(sm), C.byref(total), C.byref(free)))
+    assert sm.value >= 100 and 0 < free.value <= total.value and total.value > 100 << 30
+    ln = LayerNorm(256)
+    x = np.random.default_rng(3).standard_normal((512, 256), dtype=np.float32)
+    ln.forward(x)
+    ms = C.c_float(-1.0)
+    check(lib.tlnn_prof_begin(ctx))
+    check(lib.tlnn_prof_classes(ctx, 1))
+    before = backend.launch_count()
+    for _ in range(3):
+        y = ln.forward(x)
+    check(lib.tlnn_prof_end(ctx, C.byref(ms)))
+    rows = (_lib.ProfRow * 32)()
+    n = lib.tlnn_prof_table(ctx, rows, 32)
+    check(lib.tlnn_prof_classes(ctx, 0))
+    assert ms.value > 0.0 and backend.launch_count() - before >= 3
+    table = {r.name.decode(): (r.launches, r.ms) for r in rows[:n]}
+    assert any(k.startswith("layernorm") and v[0] == 3 and v[1] > 0 for k, v in table.items()), table
+    # asynchronous copy back into pinned memory, completed by tlnn_sync
+    hp = C.c_void_p()
+    check(lib.tlnn_host_alloc(y.nbytes, C.byref(hp)))
+    try:
+        host = np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_float)), shape=y.shape)
+        host[...] = 0
+        check(lib.tlnn_d2h_async(ctx, hp, y.ptr, y.nbytes))
+        check(lib.tlnn_sync(ctx))
+        assert np.array_equal(host, y.get())
+    finally:
+        lib.tlnn_host_free(hp)

@@ -109,7 +109,10 @@ def c3(engine):
 
 
 def _check_large(spec, net, g, n_seq, tolname):
-    x = wl.make_inputs(spec, n_seq)
+    """The first n_seq sequences of the fixture, run as one batch.  Sequence s of a fixture is global row
+    global_rows[s] of the configuration's batch."""
+    rows = (g["global_rows"] if "global_rows" in g.files else np.arange(int(g["n_seq"])))[:n_seq]
+    x = wl.make_inputs(spec)[rows]
     logits = net.predict_logits(x).get()
     tokens = net.predict_tokens(x).get()
     diffs = 0
@@ -152,7 +155,7 @@ def test_c3_live_oracle_one_sequence(engine, c3):
     assert np.abs(y - ref).max() < TOL["bf16"] * np.abs(ref).max()
 
 
-def test_c3_full_batch_properties(engine, c3):
+def test_c3_full_batch_properties(engine, golden, c3):
     """Full configuration size (16 x 1024): batch rows are independent, so the tokens of the whole batch must equal
     the tokens of each row run alone; and the causal prefix property must hold."""
     spec, net = c3
@@ -163,8 +166,15 @@ def test_c3_full_batch_properties(engine, c3):
     alone = net.predict_tokens(x[5:6]).get()
     assert np.array_equal(full[5], alone[0])
     prefix = net.predict_tokens(x[:2, :300]).get()
-    # a prefix sees the same keys: logits equal up to tile-order rounding, tokens equal except on near-ties
-    assert (prefix != full[:2, :300]).mean() < 0.02
+    # a prefix sees the same keys: logits equal up to tile-order rounding, so tokens may differ only where the
+    # reference's own top-2 gap is inside the tolerance (rows 0 and 1 are sequences 0 and 1 of the fixture)
+    g = golden("c3")
+    for s in range(2):
+        p = f"seq{s}_"
+        tol = TOL["bf16"] * float(g[p + "max_abs"])
+        differ = prefix[s] != full[s, :300]
+        excused = (g[p + "top"][:300] - g[p + "second"][:300]) < tol
+        assert not (differ & ~excused).any(), f"{int((differ & ~excused).sum())} tokens differ on a clear arg-max"
 
 
 def test_c5_bf16_prefill_vs_golden(engine, golden):
@@ -172,11 +182,12 @@ def test_c5_bf16_prefill_vs_golden(engine, golden):
     spec, net = build_seeded("c5")
     try:
         g = golden("c5")
-        _check_large(spec, net, g, 1, "bf16")
-        # full per-GPU shard at N=8 (8 x 2048): row 0 of the batch equals the sequence run alone
-        x = wl.make_inputs(spec, 8)
-        tok = net.predict_tokens(x).get()
-        tol = TOL["bf16"] * float(g["seq0_max_abs"])
-        _tokens_ok(tok[0], g, "seq0_", tol)
+        _check_large(spec, net, g, 2, "bf16")
+        # every pinned sequence (one per rank of an 8-way shard: global rows 0, 8, ..., 56), tokens only, run as the
+        # batch a single GPU would see
+        rows = g["global_rows"]
+        tok = net.predict_tokens(wl.make_inputs(spec)[rows]).get()
+        for s in range(len(rows)):
+            _tokens_ok(tok[s], g, f"seq{s}_", TOL["bf16"] * float(g[f"seq{s}_max_abs"]))
     finally:
         engine.set_precision("tf32")

@@ -104,3 +104,50 @@ def test_product_code_never_imports_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f"{f} imports the oracle"
                 assert "oracle/" not in text and "oracle." not in text, f"{f} reaches into the oracle"
+
+
+def test_fused_gpt_call_refuses_a_head_of_another_width():
+    """The C description of a GPT has one vocabulary size, used both as the id bound and as the head width: a Dense
+    head of any other shape must not reach the fused call (it would write past the logits buffer)."""
+    from torchless_nn_b200.network import GPTPlan
+
+    class Table:
+        vocab_size, embed_size = 65, 128
+
+    class Front:
+        embedding_table, context_length = Table(), 128
+
+    class Head:
+        class weights:
+            shape = (128, 70)
+
+    from torchless_nn_b200 import layers
+    plan = GPTPlan(Front(), [], None, Head())
+    with pytest.raises(ValueError, match="Dense head"):
+        plan.model()
+
+
+def test_basic_indexing_offsets_match_numpy_and_stay_selection_sized():
+    """Device-array indexing computes flat offsets from the strides, axis by axis (no array the size of the whole
+    tensor is built on the host): checked against NumPy on a stand-in object, no device needed."""
+    from torchless_nn_b200.device_array import DeviceArray
+
+    class Shape:
+        def __init__(self, shape):
+            self.shape, self.ndim = shape, len(shape)
+
+        def _normalised_key(self, key):
+            return DeviceArray._normalised_key(self, key)
+
+    shape = (4, 5, 6)
+    a = np.arange(np.prod(shape)).reshape(shape)
+    for key in [(0, -1), (slice(None), -1), (1,), (1, slice(2, 4)), (Ellipsis, 2), (2, Ellipsis), -1, slice(1, 4),
+                (slice(None), slice(4, 5), slice(None)), (slice(None, None, -1), 0), (slice(2, 2),), (3, 4, 5)]:
+        got = DeviceArray._basic_offsets(Shape(shape), key)
+        assert got.shape == a[key].shape and np.array_equal(got, a[key]), key
+    assert DeviceArray._basic_offsets(Shape(shape), (np.array([0, 1]),)) is None      # advanced index: other path
+    with pytest.raises(IndexError):
+        DeviceArray._basic_offsets(Shape(shape), (4,))
+    big = Shape((64, 2048, 50257))                                                    # the predict(x)[0, -1] idiom
+    got = DeviceArray._basic_offsets(big, (0, -1))
+    assert got.shape == (50257,) and got[0] == 2047 * 50257

@@ -12,6 +12,15 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
+def _free_bytes(ctx) -> int:
+    import ctypes as C
+    from torchless_nn_b200._lib import lib, check
+    free = C.c_size_t()
+    check(lib.tlnn_sync(ctx))
+    check(lib.tlnn_device_info(ctx, None, None, C.byref(free)))
+    return int(free.value)
+
+
 @pytest.mark.parametrize("prec", ["bf16", "tf32"])
 def test_noalloc_head_matches_regular_head_twice(engine, prec):
     from torchless_nn_b200 import _lib
@@ -36,6 +45,12 @@ def test_noalloc_head_matches_regular_head_twice(engine, prec):
             check(lib.tlnn_logits_tokens_noalloc(ctx, code, x.ptr, head.ptr(), bias.ptr, got.ptr, rows, d, vocab))
             w, g = want.get(), got.get()
             assert np.array_equal(g, w)
+            # the promise itself: a warmed call leaves the device's free memory exactly where it was
+            before = _free_bytes(ctx)
+            check(lib.tlnn_logits_tokens_noalloc(ctx, code, x.ptr, head.ptr(), bias.ptr, got.ptr, rows, d, vocab))
+            check(lib.tlnn_sync(ctx))
+            assert _free_bytes(ctx) == before
+            assert np.array_equal(got.get(), w)
             # and both agree with a float64 product wherever the top-2 gap is clear of the mode's rounding
             ref = x.get().astype(np.float64) @ table.get().astype(np.float64).T + bias.get()
             order = np.sort(ref, axis=1)

@@ -95,6 +95,14 @@ PROTOTYPES = {
     "tlnn_decode_first_sampled": (C.c_int, [vp, C.c_float, vp, vp]),
     "tlnn_decode_run_sampled": (C.c_int, [vp, vp, C.c_int, C.c_float, vp, vp]),
     "tlnn_decode_end": (C.c_int, [vp]),
+    "tlnn_comm_nccl_version": (C.c_int, [C.POINTER(C.c_int)]),
+    "tlnn_comm_unique_id": (C.c_int, [vp]),
+    "tlnn_comm_init": (C.c_int, [vp, vp, C.c_int, C.c_int, c_void_pp]),
+    "tlnn_comm_rank": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tlnn_allgather_tokens": (C.c_int, [vp, vp, vp, ll, C.POINTER(ll)]),
+    "tlnn_allgather_logits": (C.c_int, [vp, vp, vp, ll, C.POINTER(ll)]),
+    "tlnn_comm_barrier": (C.c_int, [vp]),
+    "tlnn_comm_destroy": (C.c_int, [vp]),
     "tlnn_prof_begin": (C.c_int, [vp]),
     "tlnn_prof_end": (C.c_int, [vp, C.POINTER(C.c_float)]),
     "tlnn_prof_classes": (C.c_int, [vp, C.c_int]),

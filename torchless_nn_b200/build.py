@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtlnn.so")
-SOURCES = ["api.cu", "rowops.cu", "gemm_tcgen05.cu", "attention.cu", "attention_tcgen05.cu", "layers.cu", "decode.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "rowops.cu", "gemm_tcgen05.cu", "attention.cu", "attention_tcgen05.cu", "layers.cu", "decode.cu", "noalloc.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
@@ -61,7 +61,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         print("\n".join(logs))
     objs = [os.path.join(OBJ, s.replace(".cu", ".o")) for s in SOURCES]
     if force or jobs or _stale(LIB, objs):
-        run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"])
+        run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl"])
     return LIB
 
 

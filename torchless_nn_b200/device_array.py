@@ -129,8 +129,55 @@ class DeviceArray:
             raise ValueError(f"cannot reshape array of size {self.size} into shape {tuple(shape)}")
         return DeviceArray(shape, self.dtype, ptr=self.ptr, root=self._root)
 
+    def _normalised_key(self, key):
+        """``key`` as one entry per axis (Ellipsis expanded, trailing axes filled with full slices), or None when it
+        holds anything other than integers and slices."""
+        if not isinstance(key, tuple):
+            key = (key,)
+        n_ell = sum(1 for k in key if k is Ellipsis)
+        if n_ell > 1:
+            return None
+        if n_ell:
+            i = next(j for j, k in enumerate(key) if k is Ellipsis)
+            key = key[:i] + (slice(None),) * (self.ndim - (len(key) - 1)) + key[i + 1:]
+        if len(key) > self.ndim:
+            raise IndexError(f"too many indices for array: array is {self.ndim}-dimensional, but {len(key)} were indexed")
+        key = key + (slice(None),) * (self.ndim - len(key))
+        for k in key:
+            if isinstance(k, (bool, np.bool_)) or not isinstance(k, (int, np.integer, slice)):
+                return None
+        return key
+
+    def _basic_offsets(self, key):
+        """Flat element offsets selected by integers and slices, computed from the strides axis by axis: the host
+        builds an array the size of the SELECTION, never of the whole array (``predict(x)[0, -1]`` on a
+        (64, 2048, 50257) array touches 50257 offsets).  Returns None for advanced (array, boolean) indices."""
+        key = self._normalised_key(key)
+        if key is None:
+            return None
+        strides = [1] * self.ndim
+        for ax in range(self.ndim - 2, -1, -1):
+            strides[ax] = strides[ax + 1] * self.shape[ax + 1]
+        base, axes = 0, []
+        for ax, k in enumerate(key):
+            n = self.shape[ax]
+            if isinstance(k, slice):
+                axes.append(np.arange(*k.indices(n), dtype=np.int64) * strides[ax])
+            else:
+                i = int(k) + n if k < 0 else int(k)
+                if not 0 <= i < n:
+                    raise IndexError(f"index {int(k)} is out of bounds for axis {ax} with size {n}")
+                base += i * strides[ax]
+        out = np.full((), base, dtype=np.int64)
+        for a in axes:
+            out = out[..., None] + a
+        return out
+
     def _flat_index(self, key) -> np.ndarray:
-        """Flat element offsets selected by a NumPy basic/advanced index (host-side arithmetic)."""
+        """Flat element offsets selected by a NumPy basic or advanced index (host-side arithmetic)."""
+        idx = self._basic_offsets(key)
+        if idx is not None:
+            return idx
         return np.arange(self.size, dtype=np.int64).reshape(self.shape)[key]
 
     def __getitem__(self, key):
@@ -139,17 +186,17 @@ class DeviceArray:
         idx = self._flat_index(key)
         out_shape = idx.shape
         flat = np.ascontiguousarray(idx.reshape(-1))
+        # one contiguous run is a plain copy; anything else goes through the gather kernel
+        if flat.size <= 1 or (int(flat[-1]) - int(flat[0]) == flat.size - 1 and np.all(np.diff(flat) == 1)):
+            out = DeviceArray(out_shape, self.dtype)
+            if flat.size:
+                check(lib.tlnn_d2d(backend.ctx(), out.ptr, self.ptr + int(flat[0]) * self.dtype.itemsize, out.nbytes))
+            return out
         if self.dtype != np.float32:
             return DeviceArray.from_numpy(self.get().reshape(-1)[flat].reshape(out_shape))
-        # contiguous selections are plain copies; anything else goes through the gather kernel
         out = DeviceArray(out_shape, self.dtype)
-        if flat.size == 0:
-            return out
-        if flat.size == 1 or np.all(np.diff(flat) == 1):
-            check(lib.tlnn_d2d(backend.ctx(), out.ptr, self.ptr + int(flat[0]) * 4, out.nbytes))
-        else:
-            dev_idx = DeviceArray.from_numpy(flat)
-            check(lib.tlnn_gather_f32(backend.ctx(), self.ptr, dev_idx.ptr, out.ptr, flat.size))
+        dev_idx = DeviceArray.from_numpy(flat)
+        check(lib.tlnn_gather_f32(backend.ctx(), self.ptr, dev_idx.ptr, out.ptr, flat.size))
         return out
 
     def __setitem__(self, key, value):

@@ -17,6 +17,7 @@ from .device_array import DeviceArray
 class HostFeed:
     def __init__(self, bytes_per_batch: int):
         self.bytes = int(bytes_per_batch)
+        self._version = 0           # device arrays yielded by batches() use the feeder as their root (see DeviceArray.version)
         self.handle = C.c_void_p()
         check(lib.tlnn_feed_create(backend.ctx(), self.bytes, C.byref(self.handle)))
         self._host = []

@@ -47,6 +47,9 @@ class GPTPlan:
             return None
         if blocks and len({(b.attn_block.embedding_dim, b.attn_block.num_heads, b.ffn.act_code()) for b in blocks}) != 1:
             return None
+        table = ls[0].embedding_table
+        if isinstance(ls[-1], Dense) and tuple(ls[-1].weights.shape) != (table.embed_size, table.vocab_size):
+            return None          # a head of another width runs layer by layer
         return GPTPlan(ls[0], blocks, ls[-2], ls[-1])
 
     def model(self):
@@ -61,14 +64,25 @@ class GPTPlan:
             if self.head.embedding_table.embed_size != d:
                 raise ValueError("tied head width differs from the model width")
         else:
+            # the C description has one vocabulary size: the id bound of the table and the width of the head product
+            if tuple(self.head.weights.shape) != (d, V):
+                raise ValueError(f"the fused GPT call needs a Dense head of shape ({d}, {V}); this one is "
+                                 f"{tuple(self.head.weights.shape)}")
             head_t, head_b = self.head._w.ptr(), self.head.bias.ptr
-            V = self.head.weights.shape[1]
         heads = self.blocks[0].attn_block.num_heads if self.blocks else 1
         act = self.blocks[0].ffn.act_code() if self.blocks else _lib.ACT_NONE
         m = _lib.GPTModel(f.embedding_table.vocab_size, f.context_length, d, heads, len(self.blocks), act,
                           backend.precision_code(), f.embedding_table.table.ptr, f.pos_embedding_table.ptr,
                           arr, self.final_norm.gamma.ptr, self.final_norm.beta.ptr, head_t, head_b)
         return m, arr, V
+
+
+def _rows(x, lo, hi):
+    """Rows [lo, hi) of a batch: a view for device arrays (rows are contiguous), a slice for host arrays."""
+    if isinstance(x, DeviceArray):
+        per_row = int(np.prod(x.shape[1:], dtype=np.int64)) * x.dtype.itemsize
+        return DeviceArray((hi - lo,) + tuple(x.shape[1:]), x.dtype, ptr=x.ptr + lo * per_row, root=x._root)
+    return np.asarray(x)[lo:hi]
 
 
 class CrossEntropy:
@@ -122,8 +136,14 @@ class Network:
             if isinstance(layer, Dropout) and layer.dropout_rate > 0.0 and layer.eval_mode is False:
                 raise NotImplementedError("dropout masks are training behaviour; call set_eval(True) first")
 
-    def predict_logits(self, input):
-        """Same result as ``predict`` for the GPT recipe, as one fused library call (no per-layer outputs kept)."""
+    def predict_logits(self, input, comm=None):
+        """Same result as ``predict`` for the GPT recipe, as one fused library call (no per-layer outputs kept).
+        With ``comm`` every rank runs its slice of the batch rows and the logits are all-gathered (see
+        ``predict_tokens``); for large vocabularies prefer gathering tokens."""
+        if comm is not None and comm.world > 1:
+            from .comm import sharded_rows
+            return sharded_rows(comm, len(input), lambda lo, hi: self.predict_logits(_rows(input, lo, hi)),
+                                comm.allgather_logits)
         plan = GPTPlan.match(self.layers)
         if plan is None:
             return self.predict(input)
@@ -137,8 +157,16 @@ class Network:
         check(lib.tlnn_gpt_prefill(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T, logits.ptr, None))
         return logits
 
-    def predict_tokens(self, input):
-        """arg-max of ``predict(input)`` over the last axis, int32 on the device."""
+    def predict_tokens(self, input, comm=None):
+        """arg-max of ``predict(input)`` over the last axis, int32 on the device.
+
+        With ``comm`` (a ``torchless_nn_b200.comm.Communicator``) the call is collective: every rank passes the same
+        global batch, runs the contiguous slice of rows it owns and receives the tokens of the whole batch, gathered
+        over NCCL in row order."""
+        if comm is not None and comm.world > 1:
+            from .comm import sharded_rows
+            return sharded_rows(comm, len(input), lambda lo, hi: self.predict_tokens(_rows(input, lo, hi)),
+                                comm.allgather_tokens)
         plan = GPTPlan.match(self.layers)
         if plan is not None:
             self._check_eval()
@@ -279,10 +307,32 @@ class Network:
             tokens = np.concatenate([tokens, picked.get().reshape(B, 1).astype(np.int32)], axis=1)
         return tokens
 
-    def generate_greedy(self, prompts, new_tokens: int):
+    def _last_position(self, window):
+        """Output of the model at the last position of every row of ``window`` (B, T): the blocks run on the whole
+        window, the row-wise tail (final LayerNorm, head, ...) on the last position only."""
+        split = max((i for i, l in enumerate(self.layers) if isinstance(l, TransformerBlock)), default=0) + 1
+        x = as_token_ids(window)
+        for layer in self.layers[:split]:
+            x = layer.forward(x)
+        T = x.shape[1]
+        last = x[:, T - 1:T, :] if T > 1 else x
+        for layer in self.layers[split:]:
+            last = layer.forward(last)
+        return last
+
+    def generate_greedy(self, prompts, new_tokens: int, comm=None):
         """Greedy continuation of every prompt row by ``new_tokens`` tokens; returns (B, T0 + new_tokens) int32 on
-        the device.  Prompt plus continuation must fit the context length (the notebook's sliding window beyond it,
-        demo.ipynb:1528, is not implemented)."""
+        the device.  While prompt plus continuation fit the context the steps run on the per-layer KV cache (one CUDA
+        graph replay per token).  Beyond it the notebook's sliding window applies (demo.ipynb:1528): the tokens are
+        cropped to the last ``context_length``, positions restart at the crop, and every step re-runs the window as
+        the reference does, with the arg-max of the last position appended.
+
+        With ``comm`` the call is collective: every rank passes the same prompts, decodes the rows it owns on its own
+        cache and receives all rows, gathered once at the end."""
+        if comm is not None and comm.world > 1:
+            from .comm import sharded_rows
+            return sharded_rows(comm, len(prompts), lambda lo, hi: self.generate_greedy(_rows(prompts, lo, hi), new_tokens),
+                                comm.allgather_tokens)
         plan = GPTPlan.match(self.layers)
         if plan is None:
             raise ValueError("generate_greedy needs the GPT layer recipe")
@@ -291,23 +341,28 @@ class Network:
         B, T0 = ids.shape
         if new_tokens < 1:
             raise ValueError("new_tokens must be positive")
-        if T0 + new_tokens > plan.front.context_length:
-            raise ValueError(f"prompt ({T0}) + new tokens ({new_tokens}) exceed the context length "
-                             f"{plan.front.context_length}")
-        m, keep, V = plan.model()
-        first = DeviceArray((B,), np.int32)
-        dec = C.c_void_p()
-        check(lib.tlnn_decode_begin(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T0, T0 + new_tokens,
-                                    first.ptr, C.byref(dec)))
-        try:
-            new = DeviceArray((B, new_tokens), np.int32)
-            if new_tokens > 1:
-                rest = DeviceArray((B, new_tokens - 1), np.int32)
-                check(lib.tlnn_decode_run(dec, first.ptr, new_tokens - 1, rest.ptr))
-                host = np.concatenate([first.get()[:, None], rest.get()], axis=1)
-            else:
-                host = first.get()[:, None]
-        finally:
-            lib.tlnn_decode_end(dec)
-        prompt_host = ids.get().astype(np.int32)
-        return DeviceArray.from_numpy(np.concatenate([prompt_host, host.astype(np.int32)], axis=1))
+        if T0 < 1:
+            raise ValueError("generate_greedy needs prompts of at least one token")
+        context = plan.front.context_length
+        tokens = ids.get().astype(np.int32)
+        cached = max(0, min(new_tokens, context - T0))
+        if cached >= 1:
+            m, keep, V = plan.model()
+            first = DeviceArray((B,), np.int32)
+            dec = C.c_void_p()
+            check(lib.tlnn_decode_begin(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T0, T0 + cached,
+                                        first.ptr, C.byref(dec)))
+            try:
+                new = [first.get()[:, None]]
+                if cached > 1:
+                    rest = DeviceArray((B, cached - 1), np.int32)
+                    check(lib.tlnn_decode_run(dec, first.ptr, cached - 1, rest.ptr))
+                    new.append(rest.get())
+            finally:
+                lib.tlnn_decode_end(dec)
+            tokens = np.concatenate([tokens] + [n.astype(np.int32) for n in new], axis=1)
+        for _ in range(cached, new_tokens):
+            window = tokens[:, max(0, tokens.shape[1] - context):]
+            nxt = argmax_last(self._last_position(window)).get().reshape(B, 1)
+            tokens = np.concatenate([tokens, nxt.astype(np.int32)], axis=1)
+        return DeviceArray.from_numpy(tokens)
