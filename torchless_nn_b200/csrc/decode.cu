@@ -7,6 +7,7 @@
 // GEMM with fused arg-max.  The step is weight-streaming (HBM) bound.  The current length lives in device memory and
 // every kernel of a step reads it from there, so the launch sequence of a step does not depend on the position.
 #include "common.cuh"
+#include "decode_fused.cuh"
 #include <cstdlib>
 
 namespace {
@@ -213,6 +214,10 @@ struct tlnn_decoder {
     decode_sink* d_sink = nullptr;
     int n_parts = 0;
     cudaGraphExec_t step_graph = nullptr;        // one captured step, replayed by tlnn_decode_run
+    // persistent one-launch-per-run kernel (bf16 arg-max decode, see decode_fused.cu); null pointers when it does not apply
+    tl_decode_fused_plan_t fused;
+    char* fused_mem = nullptr;
+    df_params fused_params = {};
     long long launches_per_step = 0;
     // sampling (allocated by the first sampled call): logits and probabilities (B, vocab), uniform numbers (max_len, B)
     char* sample_mem = nullptr;
@@ -308,6 +313,21 @@ int decode_one(tlnn_decoder* dec, bool sample = false, float temperature = 1.f) 
     return TLNN_OK;
 }
 
+// n_steps greedy steps in one launch; tokens_out is (B, n_cols) with column s the token of step s.
+int run_fused(tlnn_decoder* dec, int n_steps, int32_t* tokens_out, int n_cols) {
+    df_params p = dec->fused_params;
+    int done = 0;
+    while (done < n_steps) {
+        const int chunk = n_steps - done < 2048 ? n_steps - done : 2048;       // keeps the barrier counter far from wrapping
+        p.n_steps = chunk;
+        p.tokens_out = tokens_out + done;
+        p.n_cols = n_cols;
+        TL_TRY(tl_decode_fused_launch(dec->ctx, dec->fused, p));
+        done += chunk;
+    }
+    return TLNN_OK;
+}
+
 int set_sink(tlnn_decoder* dec, int32_t* tokens_out, int n_cols) {
     decode_sink h;
     h.tokens_out = tokens_out; h.n_cols = n_cols; h.pad = 0;
@@ -364,6 +384,51 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     dec->d_len = (int*)(base + o_cnt); dec->d_step = dec->d_len + 1;
     dec->d_sink = (decode_sink*)(base + o_sink);
 
+    // ---- the persistent decode kernel, where it applies: its tables and exchange buffers
+    {
+        int st = tl_decode_fused_plan(ctx, dec->m, B, max_len, &dec->fused);
+        if (st == TLNN_OK && dec->fused.ok) {
+            const tl_decode_fused_plan_t& pl = dec->fused;
+            size_t o2 = 0;
+            auto take2 = [&](size_t bytes) { size_t o = o2; o2 += (bytes + 255) & ~size_t(255); return o; };
+            const size_t f_layers = take2(sizeof(df_layer) * m->layers), f_items = take2(sizeof(df_item) * pl.items.size());
+            const size_t f_counts = take2(sizeof(int) * pl.counts.size()), f_cand = take2(sizeof(float2) * 64 * pl.grid);
+            const size_t f_bar = take2(16);
+            cudaError_t fe = cudaMalloc(&dec->fused_mem, o2);
+            if (fe != cudaSuccess) { cudaGetLastError(); dec->fused.ok = false; }
+            else {
+                std::vector<df_layer> hl(m->layers);
+                const size_t layer_elems = (size_t)B * max_len * d;
+                for (int l = 0; l < m->layers; l++) {
+                    const tlnn_block_params& bp = dec->blocks[l];
+                    df_layer& L = hl[l];
+                    L.ln1_g = bp.ln1_gamma; L.ln1_b = bp.ln1_beta; L.bqkv = bp.bqkv; L.bo = bp.bo;
+                    L.ln2_g = bp.ln2_gamma; L.ln2_b = bp.ln2_beta; L.b1 = bp.b1; L.b2 = bp.b2;
+                    L.wqkv = (const __nv_bfloat16*)bp.wqkv_t; L.wo = (const __nv_bfloat16*)bp.wo_t;
+                    L.w1 = (const __nv_bfloat16*)bp.w1_t; L.w2 = (const __nv_bfloat16*)bp.w2_t;
+                    L.kcache = (__nv_bfloat16*)dec->kcache + l * layer_elems;
+                    L.vcache = (__nv_bfloat16*)dec->vcache + l * layer_elems;
+                }
+                char* fb = dec->fused_mem;
+                fe = cudaMemcpyAsync(fb + f_layers, hl.data(), sizeof(df_layer) * hl.size(), cudaMemcpyHostToDevice, ctx->stream);
+                if (fe == cudaSuccess) fe = cudaMemcpyAsync(fb + f_items, pl.items.data(), sizeof(df_item) * pl.items.size(), cudaMemcpyHostToDevice, ctx->stream);
+                if (fe == cudaSuccess) fe = cudaMemcpyAsync(fb + f_counts, pl.counts.data(), sizeof(int) * pl.counts.size(), cudaMemcpyHostToDevice, ctx->stream);
+                if (fe == cudaSuccess) fe = cudaStreamSynchronize(ctx->stream);       // `hl` is a local
+                if (fe != cudaSuccess) { cudaGetLastError(); dec->fused.ok = false; }
+                df_params& fp = dec->fused_params;
+                fp.B = B; fp.d = d; fp.H = m->heads; fp.L = m->layers; fp.V = m->vocab; fp.max_len = max_len; fp.act = m->act;
+                fp.slot_bytes = pl.slot_bytes; fp.items_pitch = pl.items_pitch;
+                fp.layers = (const df_layer*)(fb + f_layers); fp.items = (const df_item*)(fb + f_items);
+                fp.item_counts = (const int*)(fb + f_counts);
+                fp.tok_table = m->tok_table; fp.pos_table = m->pos_table; fp.lnf_g = m->lnf_gamma; fp.lnf_b = m->lnf_beta;
+                fp.head_bias = m->head_bias; fp.head = (const __nv_bfloat16*)m->head_t;
+                fp.x = dec->x0; fp.qkv = (__nv_bfloat16*)dec->qkv; fp.att = (__nv_bfloat16*)dec->att; fp.hid = (__nv_bfloat16*)dec->hid;
+                fp.cand = (float2*)(fb + f_cand); fp.cur = dec->cur; fp.len = dec->d_len;
+                fp.bar_count = (unsigned*)(fb + f_bar); fp.abort_flag = (int*)(fb + f_bar) + 1; fp.err = ctx->d_err;
+            }
+        }
+    }
+
     // ---- prompt: the blocks of the prefill path, also filling the caches
     int status = TLNN_OK;
     do {
@@ -406,6 +471,7 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     } while (0);
     if (status) {
         cudaFree(dec->mem);
+        if (dec->fused_mem) cudaFree(dec->fused_mem);
         delete dec;
         return status;
     }
@@ -420,6 +486,11 @@ extern "C" int tlnn_decode_step(tlnn_decoder* dec, const int32_t* prev_tokens, i
     TL_REQUIRE(dec->host_len < dec->max_len, "decode: the cache is full (%d positions)", dec->max_len);
     if (prev_tokens != dec->cur)
         TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (dec->fused.ok) {
+        TL_TRY(run_fused(dec, 1, next_tokens, 1));
+        dec->host_len++;
+        return TLNN_OK;
+    }
     TL_TRY(set_sink(dec, nullptr, 0));
     TL_TRY(decode_one(dec));
     dec->host_len++;
@@ -436,6 +507,12 @@ extern "C" int tlnn_decode_run(tlnn_decoder* dec, const int32_t* prev_tokens, in
     if (n_steps == 0) return TLNN_OK;
     if (prev_tokens != dec->cur)
         TL_CUDA(cudaMemcpyAsync(dec->cur, prev_tokens, (size_t)dec->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (dec->fused.ok) {
+        // all the steps in one launch of the persistent kernel
+        TL_TRY(run_fused(dec, n_steps, tokens_out, n_steps));
+        dec->host_len += n_steps;
+        return TLNN_OK;
+    }
     TL_TRY(set_sink(dec, tokens_out, n_steps));
     TL_CUDA(cudaMemsetAsync(dec->d_step, 0, sizeof(int), ctx->stream));
     // Every kernel of a step takes the position from device memory, so one step is captured once as a CUDA graph and
@@ -552,6 +629,7 @@ extern "C" int tlnn_decode_end(tlnn_decoder* dec) {
     if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
     if (dec->sample_graph) cudaGraphExecDestroy(dec->sample_graph);
     if (dec->sample_mem) cudaFree(dec->sample_mem);
+    if (dec->fused_mem) cudaFree(dec->fused_mem);
     cudaFree(dec->mem);
     delete dec;
     return TLNN_OK;
