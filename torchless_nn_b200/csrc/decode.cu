@@ -217,6 +217,7 @@ struct tlnn_decoder {
     // persistent one-launch-per-run kernel (bf16 arg-max decode, see decode_fused.cu); null pointers when it does not apply
     tl_decode_fused_plan_t fused;
     char* fused_mem = nullptr;
+    char* fused_pack = nullptr;                  // the model's GEMM weights at the row pitch the kernel's shared-memory slots use
     df_params fused_params = {};
     long long launches_per_step = 0;
     // sampling (allocated by the first sampled call): logits and probabilities (B, vocab), uniform numbers (max_len, B)
@@ -373,7 +374,9 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     const size_t o_a = take((size_t)B * d * es), o_qkv = take((size_t)B * 3 * d * es), o_att = take((size_t)B * d * es);
     const size_t o_hid = take((size_t)B * 4 * d * es), o_parts = take((size_t)B * dec->n_parts * sizeof(float2));
     const size_t o_cur = take((size_t)B * 4), o_next = take((size_t)B * 4), o_cnt = take(16), o_sink = take(sizeof(decode_sink));
-    cudaError_t e = cudaMalloc(&dec->mem, off);
+    // the decoder's buffers come from the context's stream-ordered pool (freed blocks stay cached there, so a caller that
+    // decodes batch after batch does not pay the driver for 100s of MB of allocations each time)
+    cudaError_t e = cudaMallocAsync((void**)&dec->mem, off, ctx->stream);
     if (e != cudaSuccess) { delete dec; return tl_cuda_fail(e, "cudaMalloc(decoder)", __FILE__, __LINE__); }
     char* base = dec->mem;
     dec->kcache = base + o_k; dec->vcache = base + o_v;
@@ -386,45 +389,45 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
 
     // ---- the persistent decode kernel, where it applies: its tables and exchange buffers
     {
-        int st = tl_decode_fused_plan(ctx, dec->m, B, max_len, &dec->fused);
+        // the plan is made twice: once to learn the size of the packed weight copy, once with the allocation
+        int st = tl_decode_fused_plan(ctx, dec->m, dec->blocks.data(), B, max_len, nullptr, true, &dec->fused);
+        if (st == TLNN_OK && dec->fused.ok) {
+            bool packed = cudaMallocAsync((void**)&dec->fused_pack, dec->fused.pack_bytes, ctx->stream) == cudaSuccess;
+            if (!packed) { cudaGetLastError(); dec->fused_pack = nullptr; }
+            st = tl_decode_fused_plan(ctx, dec->m, dec->blocks.data(), B, max_len, dec->fused_pack, packed, &dec->fused);
+            for (const df_pack_job& j : dec->fused.pack_jobs) {
+                if (cudaMemcpy2DAsync(dec->fused_pack + j.dst_off, (size_t)(d + 8) * 2, j.src, j.src_pitch, j.width, j.rows,
+                                      cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess) {
+                    cudaGetLastError();
+                    dec->fused.ok = false;
+                    break;
+                }
+            }
+        }
         if (st == TLNN_OK && dec->fused.ok) {
             const tl_decode_fused_plan_t& pl = dec->fused;
             size_t o2 = 0;
             auto take2 = [&](size_t bytes) { size_t o = o2; o2 += (bytes + 255) & ~size_t(255); return o; };
-            const size_t f_layers = take2(sizeof(df_layer) * m->layers), f_items = take2(sizeof(df_item) * pl.items.size());
+            const size_t f_items = take2(sizeof(df_item) * pl.items.size());
             const size_t f_counts = take2(sizeof(int) * pl.counts.size()), f_cand = take2(sizeof(float2) * 64 * pl.grid);
-            const size_t f_bar = take2(16);
-            cudaError_t fe = cudaMalloc(&dec->fused_mem, o2);
+            const size_t f_bar = take2(4096);
+            cudaError_t fe = cudaMallocAsync((void**)&dec->fused_mem, o2, ctx->stream);
             if (fe != cudaSuccess) { cudaGetLastError(); dec->fused.ok = false; }
             else {
-                std::vector<df_layer> hl(m->layers);
-                const size_t layer_elems = (size_t)B * max_len * d;
-                for (int l = 0; l < m->layers; l++) {
-                    const tlnn_block_params& bp = dec->blocks[l];
-                    df_layer& L = hl[l];
-                    L.ln1_g = bp.ln1_gamma; L.ln1_b = bp.ln1_beta; L.bqkv = bp.bqkv; L.bo = bp.bo;
-                    L.ln2_g = bp.ln2_gamma; L.ln2_b = bp.ln2_beta; L.b1 = bp.b1; L.b2 = bp.b2;
-                    L.wqkv = (const __nv_bfloat16*)bp.wqkv_t; L.wo = (const __nv_bfloat16*)bp.wo_t;
-                    L.w1 = (const __nv_bfloat16*)bp.w1_t; L.w2 = (const __nv_bfloat16*)bp.w2_t;
-                    L.kcache = (__nv_bfloat16*)dec->kcache + l * layer_elems;
-                    L.vcache = (__nv_bfloat16*)dec->vcache + l * layer_elems;
-                }
                 char* fb = dec->fused_mem;
-                fe = cudaMemcpyAsync(fb + f_layers, hl.data(), sizeof(df_layer) * hl.size(), cudaMemcpyHostToDevice, ctx->stream);
-                if (fe == cudaSuccess) fe = cudaMemcpyAsync(fb + f_items, pl.items.data(), sizeof(df_item) * pl.items.size(), cudaMemcpyHostToDevice, ctx->stream);
+                fe = cudaMemcpyAsync(fb + f_items, pl.items.data(), sizeof(df_item) * pl.items.size(), cudaMemcpyHostToDevice, ctx->stream);
                 if (fe == cudaSuccess) fe = cudaMemcpyAsync(fb + f_counts, pl.counts.data(), sizeof(int) * pl.counts.size(), cudaMemcpyHostToDevice, ctx->stream);
-                if (fe == cudaSuccess) fe = cudaStreamSynchronize(ctx->stream);       // `hl` is a local
-                if (fe != cudaSuccess) { cudaGetLastError(); dec->fused.ok = false; }
+                if (fe != cudaSuccess) { cudaGetLastError(); dec->fused.ok = false; }    // the plan's vectors outlive the copies: they belong to the decoder
                 df_params& fp = dec->fused_params;
                 fp.B = B; fp.d = d; fp.H = m->heads; fp.L = m->layers; fp.V = m->vocab; fp.max_len = max_len; fp.act = m->act;
-                fp.slot_bytes = pl.slot_bytes; fp.items_pitch = pl.items_pitch;
-                fp.layers = (const df_layer*)(fb + f_layers); fp.items = (const df_item*)(fb + f_items);
+                fp.slot_bytes = pl.slot_bytes; fp.items_pitch = pl.items_pitch; fp.a_region = pl.a_region; fp.att_ck = pl.att_ck; fp.ns = pl.ns; fp.hd = pl.hd;
+                fp.items = (const df_item*)(fb + f_items);
                 fp.item_counts = (const int*)(fb + f_counts);
-                fp.tok_table = m->tok_table; fp.pos_table = m->pos_table; fp.lnf_g = m->lnf_gamma; fp.lnf_b = m->lnf_beta;
-                fp.head_bias = m->head_bias; fp.head = (const __nv_bfloat16*)m->head_t;
+                fp.tok_table = m->tok_table; fp.pos_table = m->pos_table;
+                fp.kcache = (__nv_bfloat16*)dec->kcache; fp.vcache = (__nv_bfloat16*)dec->vcache;
                 fp.x = dec->x0; fp.qkv = (__nv_bfloat16*)dec->qkv; fp.att = (__nv_bfloat16*)dec->att; fp.hid = (__nv_bfloat16*)dec->hid;
                 fp.cand = (float2*)(fb + f_cand); fp.cur = dec->cur; fp.len = dec->d_len;
-                fp.bar_count = (unsigned*)(fb + f_bar); fp.abort_flag = (int*)(fb + f_bar) + 1; fp.err = ctx->d_err;
+                fp.bar_flags = (unsigned*)(fb + f_bar); fp.abort_flag = (int*)(fb + f_bar) + 1023; fp.err = ctx->d_err;
             }
         }
     }
@@ -470,8 +473,9 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
         dec->host_len = T0;
     } while (0);
     if (status) {
-        cudaFree(dec->mem);
-        if (dec->fused_mem) cudaFree(dec->fused_mem);
+        cudaFreeAsync(dec->mem, ctx->stream);
+        if (dec->fused_mem) cudaFreeAsync(dec->fused_mem, ctx->stream);
+        if (dec->fused_pack) cudaFreeAsync(dec->fused_pack, ctx->stream);
         delete dec;
         return status;
     }
@@ -548,7 +552,7 @@ int ensure_sampling_buffers(tlnn_decoder* dec) {
     if (dec->sample_mem) return TLNN_OK;
     const size_t row = ((size_t)dec->B * dec->m.vocab * 4 + 255) & ~size_t(255);
     const size_t un = ((size_t)dec->max_len * dec->B * 8 + 255) & ~size_t(255);
-    TL_CUDA(cudaMalloc(&dec->sample_mem, 2 * row + un));
+    TL_CUDA(cudaMallocAsync((void**)&dec->sample_mem, 2 * row + un, dec->ctx->stream));
     dec->logits = (float*)dec->sample_mem;
     dec->probs = (float*)(dec->sample_mem + row);
     dec->uniforms = (double*)(dec->sample_mem + 2 * row);
@@ -628,9 +632,11 @@ extern "C" int tlnn_decode_end(tlnn_decoder* dec) {
     cudaStreamSynchronize(dec->ctx->stream);
     if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
     if (dec->sample_graph) cudaGraphExecDestroy(dec->sample_graph);
-    if (dec->sample_mem) cudaFree(dec->sample_mem);
-    if (dec->fused_mem) cudaFree(dec->fused_mem);
-    cudaFree(dec->mem);
+    cudaStream_t st = dec->ctx->stream;
+    if (dec->sample_mem) cudaFreeAsync(dec->sample_mem, st);
+    if (dec->fused_mem) cudaFreeAsync(dec->fused_mem, st);
+    if (dec->fused_pack) cudaFreeAsync(dec->fused_pack, st);
+    cudaFreeAsync(dec->mem, st);
     delete dec;
     return TLNN_OK;
 }

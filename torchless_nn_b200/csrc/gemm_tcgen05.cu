@@ -967,3 +967,25 @@ int sm100::make_tile_map(CUtensorMap* map, bool bf16, const void* base, long lon
     return TLNN_OK;
 }
 
+
+// Row-major bf16 matrix, box of box_cols x box_rows elements, no swizzle: the tile lands in shared memory as box_rows
+// dense rows of box_cols elements (used where a consumer reads whole rows with plain shared-memory loads).
+int sm100::make_plain_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        tl_set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return TLNN_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_set_error("cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld box=%dx%d)", (int)r, rows, cols, ld, box_cols, box_rows);
+        return TLNN_ERR_CUDA;
+    }
+    return TLNN_OK;
+}

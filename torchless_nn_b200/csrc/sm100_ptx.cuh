@@ -249,5 +249,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 // `ld` elements; the box is 128 bytes of the contiguous dimension by `box_rows` rows, 128-byte swizzle, zero fill.
 int make_tile_map(CUtensorMap* map, bool bf16, const void* base, long long rows, long long cols, long long ld,
                   int box_rows);
+// Host side: 2-D tensor map over a row-major bf16 matrix, box of box_cols x box_rows elements, no swizzle, zero fill.
+int make_plain_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows);
 
 }  // namespace sm100
