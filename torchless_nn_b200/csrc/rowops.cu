@@ -263,6 +263,60 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
     for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = expf((src[c] - m) / temperature) / s;
 }
 
+// Rows of up to 65536 values are held in the registers of one block of 1024 threads (up to 64 values per thread): every
+// load of the row is in flight at once, the row is read from memory once and written once, and the exponentials are
+// computed once.  exp((x - max) / T) is evaluated as 2^((x - max) * log2(e) / T) with the hardware exponential (a few
+// float32 ulp from the reference's exp); the division by the row sum is a multiplication by its reciprocal.
+template <int PER>
+__global__ void __launch_bounds__(1024, 1) softmax_row_in_regs_kernel(const float* __restrict__ x, float* __restrict__ out, int cols, float temperature) {
+    __shared__ float red[32];
+    __shared__ float bcast;
+    tl_grid_dependency_sync();
+    const float* src = x + (long long)blockIdx.x * cols;
+    float* dst = out + (long long)blockIdx.x * cols;
+    const int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp;
+    float v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int c = threadIdx.x + i * 1024;
+        v[i] = c < cols ? __ldcs(src + c) : -INFINITY;       // streamed: nothing reads the input again
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; i++) m = fmaxf(m, v[i]);
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        float t = warp_max(red[lane]);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    m = bcast;
+    __syncthreads();
+    const float k = 1.4426950408889634f / temperature;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        v[i] = exp2f((v[i] - m) * k);                        // 0 for the padding past the row
+        s += v[i];
+    }
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        float t = warp_sum(red[lane]);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    const float inv = 1.f / bcast;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int c = threadIdx.x + i * 1024;
+        if (c < cols) __stcs(dst + c, v[i] * inv);
+    }
+}
+
 // ---- arg-max ---------------------------------------------------------------------------------------------
 // First index of the maximum, as numpy.argmax.  NaN handling: NumPy returns the first NaN; logits here are
 // finite, and a NaN row yields the first maximum among the comparable values.
@@ -276,7 +330,20 @@ __global__ void argmax_kernel(const float* __restrict__ x, long long ldx, int32_
     const float* src = x + (long long)blockIdx.x * ldx;
     float v = -INFINITY;
     int idx = 0x7fffffff;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) argmax_combine(v, idx, src[c], c);
+    // eight loads in flight per thread; values are combined in column order, so the first maximum wins as before
+    for (int c0 = threadIdx.x; c0 < cols; c0 += blockDim.x * 8) {
+        float t[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int c = c0 + u * blockDim.x;
+            t[u] = c < cols ? __ldcs(src + c) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int c = c0 + u * blockDim.x;
+            if (c < cols) argmax_combine(v, idx, t[u], c);
+        }
+    }
     int lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarp = blockDim.x / kWarp;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -482,6 +549,15 @@ extern "C" int tlnn_softmax_fwd(tlnn_ctx* ctx, const float* x, float* out, long 
     TL_NOTNULL(x); TL_NOTNULL(out);
     TL_CUDA(cudaSetDevice(ctx->device));
     int block = cols >= 8192 ? 1024 : (cols >= 1024 ? 256 : 64);
+    if (cols > 4096 && cols <= 65536) {
+        // wide rows (a vocabulary): the row in the registers of one block, one read and one write
+        const int per = (cols + 1023) / 1024;
+        if (per <= 16) TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_row_in_regs_kernel<16>, dim3((unsigned)rows), dim3(1024), 0, x, out, cols, temperature));
+        else if (per <= 32) TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_row_in_regs_kernel<32>, dim3((unsigned)rows), dim3(1024), 0, x, out, cols, temperature));
+        else if (per <= 50) TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_row_in_regs_kernel<50>, dim3((unsigned)rows), dim3(1024), 0, x, out, cols, temperature));
+        else TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_row_in_regs_kernel<64>, dim3((unsigned)rows), dim3(1024), 0, x, out, cols, temperature));
+        return TLNN_OK;
+    }
     TL_LAUNCH(ctx, "softmax", tl_launch_kernel(ctx, softmax_kernel, dim3((unsigned)rows), dim3(block), 0, x, out, cols, temperature));
     return TLNN_OK;
 }
