@@ -322,7 +322,7 @@ def class_table(ctx, fn, repeats: int = 1):
 # capture of exactly that case (dram__bytes_read.sum + dram__bytes_write.sum summed over the four launches).  Every
 # operand and output of these products is streamed once, so traffic grows in proportion to the rows; the weights
 # (25 MB per block) are the part that does not, and they are 2 % of the figure.
-GEMM_BLOCK_TRAFFIC = {"rows": 16384, "d_model": 1024, "bytes": None}
+GEMM_BLOCK_TRAFFIC = {"rows": 16384, "d_model": 1024, "bytes": 591.4e6}
 
 
 def measure_decode(args, rank, world, comm, timer):
