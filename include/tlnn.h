@@ -289,6 +289,18 @@ int tlnn_feed_destroy(tlnn_feeder* f);
  * tlnn_sync / tlnn_check reports TLNN_ERR_TIMEOUT, after which the context is clean and usable again. */
 int tlnn_selftest_wait(tlnn_ctx* ctx, int limit_ms);
 
+/* ---- memory-safety checks for test runs ------------------------------------------ */
+/* No counterpart in the reference (NumPy checks every index; a CUDA kernel does not).  Two aids stand in for a memory
+ * checker:
+ *  - canaries: after tlnn_debug_canaries(ctx, 1) every tlnn_alloc places 256 bytes of a known pattern behind the block;
+ *    tlnn_free verifies them (this waits for the stream) and tlnn_debug_check verifies every live guarded block,
+ *    returning the number of blocks found overwritten so far and the number of live guarded blocks;
+ *  - the debug build of the library (`python -m torchless_nn_b200.build --debug` -> libtlnn_debug.so, loaded by the
+ *    Python package when TLNN_DEBUG=1): the stores of the GEMM, attention and decode kernels check their offset against
+ *    the output's extent, record a violation as TLNN_ERR_INDEX (site 9xx, offending offset) and skip the store. */
+int tlnn_debug_canaries(tlnn_ctx* ctx, int enable);
+int tlnn_debug_check(tlnn_ctx* ctx, long long* corrupted, long long* guarded);
+
 /* ---- profiling -------------------------------------------------------------- */
 /* CUDA-event timing of everything enqueued between begin and end on the compute stream (milliseconds). */
 int tlnn_prof_begin(tlnn_ctx* ctx);

@@ -29,11 +29,32 @@ def golden():
 
 @pytest.fixture(scope="session")
 def engine():
-    """The device context; a GPU test fails (not skips) when the library or the GPU is missing."""
+    """The device context; a GPU test fails (not skips) when the library or the GPU is missing.  The whole GPU session
+    runs with canary-padded allocations (no memory checker is available on the test machines): every device array is
+    followed by 256 bytes of a known pattern, verified when it is freed, after every test and at the end."""
+    import ctypes as C
     from torchless_nn_b200 import backend
-    backend.ctx()
+    from torchless_nn_b200._lib import lib, check
+    ctx = backend.ctx()
+    check(lib.tlnn_debug_canaries(ctx, 1))
     yield backend
     backend.synchronize()
+    bad, live = C.c_longlong(), C.c_longlong()
+    check(lib.tlnn_debug_check(ctx, C.byref(bad), C.byref(live)))
+    assert bad.value == 0, f"{bad.value} device allocations were written past their end during the session"
+
+
+@pytest.fixture(autouse=True)
+def _canaries_intact_after_each_gpu_test(request):
+    yield
+    if request.node.get_closest_marker("gpu") is None or "engine" not in request.fixturenames:
+        return
+    import ctypes as C
+    from torchless_nn_b200 import backend
+    from torchless_nn_b200._lib import lib, check
+    bad, live = C.c_longlong(), C.c_longlong()
+    check(lib.tlnn_debug_check(backend.ctx(), C.byref(bad), C.byref(live)))
+    assert bad.value == 0, f"{request.node.name}: {bad.value} device allocations were written past their end ({live.value} guarded)"
 
 
 def rel_err(got, ref):

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtlnn.so")
+# TLNN_DEBUG=1 selects the debug build (device-side bounds checks compiled in): `python -m torchless_nn_b200.build --debug`
+LIB_PATH = os.path.join(HERE, "libtlnn_debug.so" if os.environ.get("TLNN_DEBUG") == "1" else "libtlnn.so")
 
 OK, ERR_VALUE, ERR_INDEX, ERR_CUDA, ERR_NOMEM, ERR_TIMEOUT, ERR_NULL = 0, -1, -2, -3, -4, -5, -6
 F32, BF16, I32, I64, U8 = 0, 1, 2, 3, 4
@@ -103,6 +104,8 @@ PROTOTYPES = {
     "tlnn_allgather_logits": (C.c_int, [vp, vp, vp, ll, C.POINTER(ll)]),
     "tlnn_comm_barrier": (C.c_int, [vp]),
     "tlnn_comm_destroy": (C.c_int, [vp]),
+    "tlnn_debug_canaries": (C.c_int, [vp, C.c_int]),
+    "tlnn_debug_check": (C.c_int, [vp, C.POINTER(ll), C.POINTER(ll)]),
     "tlnn_prof_begin": (C.c_int, [vp]),
     "tlnn_prof_end": (C.c_int, [vp, C.POINTER(C.c_float)]),
     "tlnn_prof_classes": (C.c_int, [vp, C.c_int]),

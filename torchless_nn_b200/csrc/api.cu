@@ -129,15 +129,59 @@ extern "C" int tlnn_alloc(tlnn_ctx* ctx, size_t bytes, void** dptr) {
     TL_NOTNULL(dptr);
     TL_CUDA(cudaSetDevice(ctx->device));
     if (bytes == 0) bytes = 16;
+    if (ctx->canaries) {
+        const size_t user = (bytes + 15) & ~size_t(15);
+        TL_CUDA(cudaMallocAsync(dptr, user + TL_CANARY_BYTES, ctx->stream));
+        TL_CUDA(cudaMemsetAsync(static_cast<char*>(*dptr) + user, TL_CANARY_BYTE, TL_CANARY_BYTES, ctx->stream));
+        ctx->live[*dptr] = user;
+        return TLNN_OK;
+    }
     TL_CUDA(cudaMallocAsync(dptr, bytes, ctx->stream));
     return TLNN_OK;
+}
+
+// 1 if the canary behind a live block is intact, 0 if not, negative status on a CUDA error (waits for the stream).
+static int canary_intact(tlnn_ctx* ctx, void* dptr, size_t user) {
+    unsigned char host[TL_CANARY_BYTES];
+    TL_CUDA(cudaMemcpyAsync(host, static_cast<char*>(dptr) + user, TL_CANARY_BYTES, cudaMemcpyDeviceToHost, ctx->stream));
+    TL_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (size_t i = 0; i < TL_CANARY_BYTES; i++)
+        if (host[i] != (unsigned char)TL_CANARY_BYTE) return 0;
+    return 1;
 }
 
 extern "C" int tlnn_free(tlnn_ctx* ctx, void* dptr) {
     TL_NOTNULL(ctx);
     if (!dptr) return TLNN_OK;
     TL_CUDA(cudaSetDevice(ctx->device));
+    auto it = ctx->live.find(dptr);
+    if (it != ctx->live.end()) {
+        const int ok = canary_intact(ctx, dptr, it->second);
+        if (ok < 0) return ok;
+        if (ok == 0) ctx->canary_failures++;
+        ctx->live.erase(it);
+    }
     TL_CUDA(cudaFreeAsync(dptr, ctx->stream));
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_debug_canaries(tlnn_ctx* ctx, int enable) {
+    TL_NOTNULL(ctx);
+    ctx->canaries = enable != 0;       // blocks allocated before stay unguarded; guarded blocks stay tracked until freed
+    return TLNN_OK;
+}
+
+extern "C" int tlnn_debug_check(tlnn_ctx* ctx, long long* corrupted, long long* guarded) {
+    TL_NOTNULL(ctx);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    long long bad = ctx->canary_failures;
+    for (auto& kv : ctx->live) {
+        const int ok = canary_intact(ctx, kv.first, kv.second);
+        if (ok < 0) return ok;
+        if (ok == 0) bad++;
+    }
+    if (corrupted) *corrupted = bad;
+    if (guarded) *guarded = (long long)ctx->live.size();
     return TLNN_OK;
 }
 

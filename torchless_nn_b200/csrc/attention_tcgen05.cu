@@ -430,7 +430,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 uint32_t acc[32];
                 tmem_ld32_issue(o_tmem + (uint32_t)(c * 32), acc);
                 tmem_ld_wait();
-                if (q_row < T) {
+                if (q_row < T && TL_DBG_IN_BOUNDS(err, (long long)(b * T + q_row) * d + h * HD + c * 32 + 32 <= (long long)n_bh / H * T * d, 920,
+                                                  (long long)(b * T + q_row) * d + h * HD + c * 32)) {
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
                         uint4 pk4;

@@ -29,6 +29,16 @@ __device__ __forceinline__ void tl_dev_fail(tlnn_dev_err* e, int code, int where
     }
 }
 
+// Debug build (-DTLNN_DEBUG, `python -m torchless_nn_b200.build --debug` -> libtlnn_debug.so): stores of the large
+// kernels check their linear offset against the extent of the output first; a violation is recorded in the error word
+// (TLNN_ERR_INDEX with the site and the offending offset, reported at the next sync) and the store is skipped - the
+// kernel never traps.  In the regular build the check compiles to nothing.
+#ifdef TLNN_DEBUG
+#define TL_DBG_IN_BOUNDS(err, cond, site, detail) ((cond) ? true : (tl_dev_fail((err), TLNN_ERR_INDEX, (site), (long long)(detail)), false))
+#else
+#define TL_DBG_IN_BOUNDS(err, cond, site, detail) (true)
+#endif
+
 // ---- profiling table ----------------------------------------------------------------------------
 struct tl_prof_pending {
     const char* name;
@@ -57,7 +67,15 @@ struct tlnn_ctx {
     std::vector<tl_prof_pending> pending;
     std::vector<cudaEvent_t> event_pool;
     std::map<std::string, std::pair<long long, double>> table;
+
+    // canary mode (tlnn_debug_canaries): every tlnn_alloc is followed by TL_CANARY_BYTES of a known pattern, checked
+    // when the block is freed and by tlnn_debug_check
+    bool canaries = false;
+    std::map<void*, size_t> live;      // user pointer -> user bytes
+    long long canary_failures = 0;
 };
+constexpr size_t TL_CANARY_BYTES = 256;
+constexpr int TL_CANARY_BYTE = 0xC5;
 
 // ---- host-side error plumbing --------------------------------------------------------------------
 void tl_set_error(const char* fmt, ...);
@@ -179,6 +197,7 @@ struct tl_gemm_epilogue {
     int out_off = 0;
     float2* argmax_partials = nullptr;  // (M, tl_gemm_argmax_parts) of (max, index as float bits) or null
     int accurate_math = 0;              // 1: activation to a few float32 ulp, 0: hardware tanh approximation
+    long long out_elems = 0;            // extent of `out` in elements, filled in by tl_gemm (checked by the debug build's stores)
 };
 
 // A (M,K) and W (N,K) both with the contraction dimension contiguous, of element kind `prec`

@@ -358,6 +358,8 @@ __device__ __noinline__ void item_epilogue(df_state& s, const df_item& it, const
             if (kind == DF_HEAD) {
                 if (v0 > best) { best = v0; best_n = n; }
                 if (has1 && v1 > best) { best = v1; best_n = n + 1; }
+            } else if (!TL_DBG_IN_BOUNDS(p.err, n + 1 < (kind == DF_QKV ? 3 : kind == DF_FFN1 ? 4 : 1) * p.d, 930 + kind, n)) {
+                // debug build only: a feature outside the product's width (recorded, store skipped)
             } else if (kind == DF_QKV) {
                 *reinterpret_cast<uint32_t*>(p.qkv + (size_t)m * 3 * p.d + n) = pack_bf16(v0, v1);
             } else if (kind == DF_FFN1) {

@@ -368,6 +368,7 @@ __device__ __forceinline__ void epilogue_warp(const tl_gemm_epilogue& ep, int M,
                             if (GENERIC && ep.row_group > 0)
                                 orow = (row / ep.row_group) * ep.out_group + ep.out_off + row % ep.row_group;
                             const long long off = orow * ep.ldo + col0 + c4 * 4;
+                            if (!TL_DBG_IN_BOUNDS(err, off >= 0 && off + 4 <= ep.out_elems, 910, off)) continue;
                             if (out_bf16) {
                                 __nv_bfloat162 h0 = __floats2bfloat162_rn(o.x, o.y);
                                 __nv_bfloat162 h1 = __floats2bfloat162_rn(o.z, o.w);
@@ -897,8 +898,14 @@ int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count) {
 }
 
 int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w, long long ldw, int M, int N, int K,
-            const tl_gemm_epilogue& ep) {
+            const tl_gemm_epilogue& ep_in) {
     if (M == 0 || N == 0) return TLNN_OK;
+    tl_gemm_epilogue ep = ep_in;
+    {
+        // extent of the output as the epilogue addresses it (rows may be remapped in groups): last row's end
+        const long long out_rows = ep.row_group > 0 ? ((long long)(M - 1) / ep.row_group) * ep.out_group + ep.out_off + (M - 1) % ep.row_group + 1 : M;
+        ep.out_elems = (out_rows - 1) * ep.ldo + N;
+    }
     TL_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad shape M=%d N=%d K=%d", M, N, K);
     const int esz = prec == TLNN_PREC_BF16 ? 2 : 4;
     TL_REQUIRE((K * esz) % 16 == 0, "gemm: the contraction length %d must be a multiple of %d elements", K, 16 / esz);
