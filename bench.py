@@ -223,6 +223,14 @@ def golden_rows_match(name: str, tokens: np.ndarray, tol_rel: float):
     if not os.path.exists(path):
         return None, 0, 0, 0
     g = np.load(path)
+    if "argmax" in g.files:
+        # a small configuration: the fixture holds the reference's result for the whole batch
+        n = min(tokens.shape[0], g["argmax"].shape[0])
+        tol = tol_rel * float(g["max_abs"])
+        differ = tokens[:n] != g["argmax"][:n]
+        excused = (g["top"][:n] - g["second"][:n]) < tol
+        n_bad = int((differ & ~excused).sum())
+        return bool(n_bad == 0), n, int(differ.sum()), n_bad
     rows = g["global_rows"] if "global_rows" in g.files else np.arange(int(g["n_seq"]))
     ok, n_diff, n_bad, checked = True, 0, 0, 0
     for s, r in enumerate(rows):

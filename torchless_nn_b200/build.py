@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtlnn.so")
-SOURCES = ["api.cu", "rowops.cu", "gemm_tcgen05.cu", "attention.cu", "attention_tcgen05.cu", "layers.cu", "decode.cu", "decode_fused.cu", "noalloc.cu", "comm.cu"]
+SOURCES = ["api.cu", "rowops.cu", "gemm_tcgen05.cu", "attention.cu", "attention_tcgen05.cu", "attention_tf32.cu", "layers.cu", "decode.cu", "decode_fused.cu", "noalloc.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

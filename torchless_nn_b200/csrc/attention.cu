@@ -620,6 +620,8 @@ int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int o
     const float* q = reinterpret_cast<const float*>(qkv);
     float* o = reinterpret_cast<float*>(out);
     const int round_out = out_kind == TL_OUT_TF32;
+    if (tl_attention_tf32_applies(T, hd) && (reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0)
+        return tl_attention_tf32(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 8) return launch_f32<8>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 16) return launch_f32<16>(ctx, q, o, B, T, heads, causal, round_out);
     if (hd == 32) return launch_f32<32>(ctx, q, o, B, T, heads, causal, round_out);

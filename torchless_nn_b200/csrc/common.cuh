@@ -214,6 +214,11 @@ int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count);
 int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int out_kind,
                       int B, int T, int heads, int hd, int causal);
 
+// FP32/TF32-mode attention on the tensor cores (attention_tf32.cu): whether a shape takes it - its projection should then
+// round q, k and v to TF32 - and the launcher.
+bool tl_attention_tf32_applies(int T, int hd);
+int tl_attention_tf32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int heads, int causal, int round_out);
+
 // Copy the K and V thirds of a packed (B*T, 3d) projection into per-layer caches laid out (B, cache_len, d).
 int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int cache_len);
 int tl_run_block_kv(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,

@@ -90,7 +90,8 @@ int run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* 
     TL_TRY(tl_layernorm(ctx, x, p->ln1_gamma, p->ln1_beta, 1e-5f, a, kind, M, d));
     tl_gemm_epilogue e1;
     e1.bias = p->bqkv; e1.out = qkv; e1.ldo = 3 * d;
-    e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_F32;    // float32 attention reads unrounded q, k, v
+    // the exact float32 attention kernels read unrounded q, k, v; the tensor-core one wants them rounded to TF32
+    e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : (tl_attention_tf32_applies(T, d / heads) ? TL_OUT_TF32 : TL_OUT_F32);
     TL_TRY(tl_gemm(ctx, prec, a, d, p->wqkv_t, d, (int)M, 3 * d, d, e1));
     if (kcache) TL_TRY(tl_kv_store(ctx, prec, qkv, kcache, vcache, B, T, d, cache_len));
     TL_TRY(tl_attention_core(ctx, prec, qkv, att, kind, B, T, heads, d / heads, causal));
@@ -187,7 +188,8 @@ extern "C" int tlnn_attention_fwd(tlnn_ctx* ctx, int prec, const float* x, const
     const int kind = op_kind(prec);
     TL_TRY(tl_convert(ctx, x, d, a, kind, M, d));
     tl_gemm_epilogue e1;
-    e1.bias = bqkv; e1.out = qkv; e1.ldo = 3 * d; e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OUT_F32;
+    e1.bias = bqkv; e1.out = qkv; e1.ldo = 3 * d;
+    e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : (tl_attention_tf32_applies(T, d / heads) ? TL_OUT_TF32 : TL_OUT_F32);
     TL_TRY(tl_gemm(ctx, prec, a, d, wqkv_t, d, (int)M, 3 * d, d, e1));
     TL_TRY(tl_attention_core(ctx, prec, qkv, att, kind, B, T, heads, d / heads, causal));
     tl_gemm_epilogue e2;
