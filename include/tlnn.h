@@ -214,6 +214,22 @@ typedef struct {
 int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T,
                      float* logits, int32_t* tokens);
 
+/* Network.predict (network.py:33-39) for the ViT recipe of the notebook (demo.ipynb, the ViT cell): VitProjector,
+ * L encoder blocks, final LayerNorm, VitMLPHead.  One call enqueues the whole forward and writes the class scores
+ * out (B, n_out) float32.  img (B, channels, height, width) float32; proj_t, cls_reg and pos as in
+ * tlnn_vit_project_fwd; head_t prepared (n_out, d); head_bias (n_out) or NULL.  The final LayerNorm is applied to the
+ * class row of every image only - LayerNorm works row by row and VitMLPHead (transformer_adapters.py:89-95) reads no
+ * other row - so the scores equal those of the layer-by-layer calls.  A repeated identical call replays a captured
+ * CUDA graph, like tlnn_gpt_prefill. */
+typedef struct {
+    int channels, height, width, patch_h, patch_w, d, heads, layers, act, prec, registers, n_out;
+    const void* proj_t; const float* cls_reg; const float* pos;
+    const tlnn_block_params* blocks;
+    const float* lnf_gamma; const float* lnf_beta;
+    const void* head_t; const float* head_bias;
+} tlnn_vit_model;
+int tlnn_vit_forward(tlnn_ctx* ctx, const tlnn_vit_model* m, const float* img, int B, float* out);
+
 /* ---- greedy decode with a per-layer KV cache ------------------------------- */
 /* Replaces the generation loop of demo.ipynb:1520-1535 (which re-runs the whole window for every token)
  * with arg-max sampling.  `tlnn_decode_begin` runs the prompts (B, T0) through the model, fills the cache

@@ -100,6 +100,54 @@ def test_c2_vit_vs_golden(engine, golden):
         engine.set_precision("tf32")
 
 
+def test_c2_vit_fused_forward(engine, golden):
+    """The whole-model call (tlnn_vit_forward) against the fixture, against the layer-by-layer path, on repeated calls
+    (plain launches, capture, graph replay), on an odd batch, in both precision modes and with registers."""
+    from torchless_nn_b200.models import build_seeded
+    from torchless_nn_b200.network import Network, ViTPlan
+    from torchless_nn_b200.backend import xp
+    spec, net = build_seeded("c2")
+    assert ViTPlan.match(net.layers) is not None
+    g = golden("c2")
+    x = wl.make_inputs(spec)
+    tol = TOL["tf32"] * float(g["max_abs"])
+    xd = xp.array(x)
+    layerwise = net.predict(xd).get()
+    runs = [net.predict_logits(xd).get() for _ in range(4)]          # 1: plain, 2: captured, 3-4: replayed
+    for y in runs:
+        assert y.shape == (256, 10)
+        assert np.abs(y - g["logits"]).max() < tol
+        assert np.array_equal(y, runs[0])
+    # same kernels on the same rows as the layer-by-layer path, except that only the class rows are normalised
+    assert np.abs(runs[0] - layerwise).max() < 1e-5 * float(g["max_abs"])
+    tok = net.predict_tokens(xd).get()
+    assert tok.dtype == np.int32 and tok.shape == (256,)
+    _tokens_ok(tok, g, "", tol)
+    y7 = net.predict_logits(x[:7]).get()
+    assert np.abs(y7 - g["logits"][:7]).max() < tol
+    assert net.predict_logits(x[:0]).shape == (0, 10)
+    with pytest.raises(ValueError):
+        net.predict_logits(x[:, :, :16])
+    engine.set_precision("bf16")
+    try:
+        yb = net.predict_logits(xd).get()
+        assert np.abs(yb - g["logits"]).max() < TOL["bf16"] * float(g["max_abs"])
+        assert np.abs(yb - net.predict(xd).get()).max() < 1e-5 * float(g["max_abs"])
+    finally:
+        engine.set_precision("tf32")
+    # registers and the demo's 2 x 2 patches of a 3-channel image (feature width 12, padded to 16): against the oracle
+    from torchless_nn_b200.layers import TransformerBlock, LayerNorm
+    from torchless_nn_b200.transformer_adapters import VitProjector, VitMLPHead
+    from torchless_nn_b200.activations import GeLU
+    small = Network([VitProjector((3, 8, 8), (2, 2), 32, num_registers=2), TransformerBlock(32, 19, 4, GeLU),
+                     LayerNorm(32), VitMLPHead(32, 5)])
+    small.set_eval(True)
+    img = np.random.default_rng(3).standard_normal((6, 3, 8, 8)).astype(np.float32)
+    a, b = small.predict(img).get(), small.predict_logits(img).get()
+    assert a.shape == b.shape == (6, 5)
+    assert np.abs(a - b).max() < 1e-5 * np.abs(a).max()
+
+
 @pytest.fixture(scope="module")
 def c3(engine):
     from torchless_nn_b200.models import build_seeded

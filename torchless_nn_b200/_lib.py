@@ -36,6 +36,14 @@ class GPTModel(C.Structure):
                 ("lnf_gamma", vp), ("lnf_beta", vp), ("head_t", vp), ("head_bias", vp)]
 
 
+class ViTModel(C.Structure):
+    """tlnn_vit_model."""
+    _fields_ = [(n, C.c_int) for n in ("channels", "height", "width", "patch_h", "patch_w", "d", "heads", "layers", "act",
+                                       "prec", "registers", "n_out")] + \
+               [("proj_t", vp), ("cls_reg", vp), ("pos", vp), ("blocks", C.POINTER(BlockParams)),
+                ("lnf_gamma", vp), ("lnf_beta", vp), ("head_t", vp), ("head_bias", vp)]
+
+
 class ProfRow(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("launches", ll), ("ms", C.c_double)]
 
@@ -89,6 +97,7 @@ PROTOTYPES = {
     "tlnn_logits_tokens_noalloc": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, ll, C.c_int, C.c_int]),
     "tlnn_vit_project_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp] + [C.c_int] * 8),
     "tlnn_vit_head_fwd": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tlnn_vit_forward": (C.c_int, [vp, C.POINTER(ViTModel), vp, C.c_int, vp]),
     "tlnn_gpt_prefill": (C.c_int, [vp, C.POINTER(GPTModel), vp, C.c_int, C.c_int, C.c_int, vp, vp]),
     "tlnn_decode_begin": (C.c_int, [vp, C.POINTER(GPTModel), vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, c_void_pp]),
     "tlnn_decode_step": (C.c_int, [vp, vp, vp]),

@@ -455,20 +455,6 @@ __device__ __noinline__ bool run_item(df_state& s, const df_item& it, int step) 
 
 // All items of this CTA that belong to (kind, layer) at the head of its list.
 __device__ bool run_phase(df_state& s, int kind, int layer, int step) {
-    if (s.p.pad2 & (1 << kind)) {      // experiments: consume the phase's items without computing (results are garbage)
-        const long long step_end0 = (long long)(step + 1) * s.n_items;
-        while (s.cons < step_end0) {
-            const df_item it = s.items[s.cons % s.n_items];
-            if (it.kind != kind || (kind != DF_HEAD && it.layer != layer)) break;
-            const long long cons = s.cons, prod = s.prod;
-            if (!df_wait(&s.full[cons & 1], (uint32_t)((cons >> 1) & 1), s.s_abort, s.p.err, 703)) return false;
-            __syncthreads();
-            issue_item(s, prod);
-            if (threadIdx.x == 0) { s.prod = prod + 1; s.cons = cons + 1; }
-            __syncthreads();
-        }
-        return true;
-    }
     const long long step_end = (long long)(step + 1) * s.n_items;          // never run into the next step's items
     while (s.cons < step_end) {
         const df_item& it = s.items[s.cons % s.n_items];       // read in place (shared memory for all but the largest models)
@@ -674,7 +660,7 @@ __device__ __noinline__ bool attention_phase(df_state& s, int layer, int pos) {
 // phases ahead, the HBM reads overlap the latency-bound products in between.  CTA c < 2 B takes (sequence c / 2, keys or
 // values); one thread issues the requests, 64 KB apiece.
 __device__ void prefetch_cache(const df_params& p, int layer, int pos) {
-    if ((int)blockIdx.x >= 2 * p.B || threadIdx.x != 32 || pos <= 0 || (p.pad2 & 64)) return;
+    if ((int)blockIdx.x >= 2 * p.B || threadIdx.x != 32 || pos <= 0) return;
     const int b = blockIdx.x >> 1;
     const bf16* base = ((blockIdx.x & 1) ? p.vcache : p.kcache) + ((size_t)layer * p.B + b) * p.max_len * p.d;
     const size_t bytes = (size_t)pos * p.d * 2;
@@ -775,11 +761,9 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_fused_kernel(const df_pa
             alive = alive && grid_sync(s);
             lap(1);
             if (!alive) break;
-            if (!(p.pad2 & 32)) {
-                if (p.hd == 64) alive = attention_phase<64>(s, l, pos);
-                else if (p.hd == 32) alive = attention_phase<32>(s, l, pos);
-                else alive = attention_phase<128>(s, l, pos);
-            }
+            if (p.hd == 64) alive = attention_phase<64>(s, l, pos);
+            else if (p.hd == 32) alive = attention_phase<32>(s, l, pos);
+            else alive = attention_phase<128>(s, l, pos);
             lap(2);
             alive = alive && grid_sync(s);
             lap(3);
@@ -896,13 +880,11 @@ int tl_decode_fused_plan(tlnn_ctx* ctx, const tlnn_gpt_model& m, const tlnn_bloc
     const long long budget = ((long long)dev_smem - 256 - DF_TAIL_BYTES - (long long)a_bytes) / 2 - (long long)d * 8;
     int ns = (int)(budget / (lda * 2 + 4) / 16) * 16;
     if (ns > 64) ns = 64;
-    if (const char* e = getenv("TLNN_DF_NS")) { const int v = atoi(e); if (v >= 16 && v <= ns && v % 16 == 0) ns = v; }   // experiments
     if (ns < 16) return TLNN_OK;
     plan->ns = ns;
     plan->slot_bytes = ns * lda * 2 + ns * 4 + d * 8;
     plan->smem = a_bytes + 2 * (size_t)plan->slot_bytes + DF_TAIL_BYTES;
     plan->grid = ctx->sm_count;
-    if (const char* e = getenv("TLNN_DF_GRID")) { const int v = atoi(e); if (v >= 64 && v <= ctx->sm_count) plan->grid = v; }   // experiments
     // the work items of one step, dealt round-robin over the CTAs in phase order
     std::vector<std::vector<df_item>> per(plan->grid);
     long long next = 0;
@@ -965,7 +947,6 @@ int tl_decode_fused_launch(tlnn_ctx* ctx, const tl_decode_fused_plan_t& plan, co
     }
     TL_CUDA(cudaMemsetAsync(params.bar_flags, 0, 4096, ctx->stream));      // barrier flags (one word per CTA) and the abort flag
     df_params p = params;
-    if (const char* e = getenv("TLNN_DF_SKIP")) p.pad2 = atoi(e);       // experiments
     CUtensorMap kmap, vmap;
     const long long cache_rows = (long long)p.L * p.B * p.max_len;
     TL_TRY(sm100::make_plain_map(&kmap, p.kcache, cache_rows, p.d, p.d, p.hd, p.att_ck));

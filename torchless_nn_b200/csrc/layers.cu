@@ -276,26 +276,26 @@ extern "C" int tlnn_norm_logits_fwd(tlnn_ctx* ctx, int prec, const float* x, con
     return run_head(ctx, prec, a, table_t, bias, logits, tokens, rows, d, vocab, cur);
 }
 
-extern "C" int tlnn_vit_project_fwd(tlnn_ctx* ctx, int prec, const float* img, const void* proj_t, const float* cls_reg,
-                                    const float* pos, float* out, int B, int C, int H, int W, int ph, int pw, int d, int regs) {
-    TL_NOTNULL(ctx); TL_NOTNULL(proj_t); TL_NOTNULL(cls_reg); TL_NOTNULL(pos); TL_NOTNULL(out);
-    TL_REQUIRE(prec_ok(prec), "unknown precision %d", prec);
-    TL_REQUIRE(B >= 0 && C > 0 && H > 0 && W > 0 && ph > 0 && pw > 0 && d > 0 && regs >= 0, "vit_project: bad shape");
-    TL_REQUIRE(H % ph == 0 && W % pw == 0, "vit_project: image %dx%d is not a multiple of the patch %dx%d", H, W, ph, pw);
+namespace {
+
+// Operand row pitch of the patch matrix: a patch feature width that is not a multiple of 8 (the demo's 2 x 2 x 3 = 12)
+// is padded with zero columns on both operands, because the GEMM wants operand rows of a multiple of 16 bytes.
+inline int vit_patch_pitch(int tdim) { return (tdim + 7) / 8 * 8; }
+
+size_t vit_project_ws_bytes(int prec, long long M, int d, int tdim) {
+    const int ldt = vit_patch_pitch(tdim);
+    return tl_ws_round((size_t)M * ldt * op_size(prec)) + tl_ws_round((size_t)d * ldt * op_size(prec));
+}
+
+// Everything the projector enqueues; the pieces come from `cur`, which the caller has reserved.
+int vit_project_enqueue(tlnn_ctx* ctx, int prec, const float* img, const void* proj_t, const float* cls_reg, const float* pos,
+                        float* out, int B, int C, int H, int W, int ph, int pw, int d, int regs, tl_ws_cursor cur) {
     const int tdim = ph * pw * C, n_patch = (H / ph) * (W / pw), n_cls = 1 + regs, T = n_cls + n_patch;
-    if (B == 0) return TLNN_OK;
-    TL_NOTNULL(img);
-    TL_CUDA(cudaSetDevice(ctx->device));
     const long long M = (long long)B * n_patch;
-    // A patch feature width that is not a multiple of 8 (the demo's 2 x 2 x 3 = 12) is padded with zero columns on
-    // both operands: the GEMM wants operand rows of a multiple of 16 bytes.
-    const int ldt = (tdim + 7) / 8 * 8;
-    const bool padded = ldt != tdim;
-    TL_TRY(tl_ws_reserve(ctx, tl_ws_round((size_t)M * ldt * op_size(prec)) + tl_ws_round((size_t)d * ldt * op_size(prec))));
-    tl_ws_cursor cur(ctx);
+    const int ldt = vit_patch_pitch(tdim);
     void* tok = cur.take<char>((size_t)M * ldt * op_size(prec));
     const void* weight = proj_t;
-    if (padded) {
+    if (ldt != tdim) {
         void* wp = cur.take<char>((size_t)d * ldt * op_size(prec));
         size_t n = (size_t)d * ldt;
         int grid = (int)((n + 255) / 256);
@@ -323,6 +323,27 @@ extern "C" int tlnn_vit_project_fwd(tlnn_ctx* ctx, int prec, const float* img, c
     return TLNN_OK;
 }
 
+int check_vit_image(int B, int C, int H, int W, int ph, int pw, int d, int regs) {
+    TL_REQUIRE(B >= 0 && C > 0 && H > 0 && W > 0 && ph > 0 && pw > 0 && d > 0 && regs >= 0, "vit_project: bad shape");
+    TL_REQUIRE(H % ph == 0 && W % pw == 0, "vit_project: image %dx%d is not a multiple of the patch %dx%d", H, W, ph, pw);
+    return TLNN_OK;
+}
+
+}  // namespace
+
+extern "C" int tlnn_vit_project_fwd(tlnn_ctx* ctx, int prec, const float* img, const void* proj_t, const float* cls_reg,
+                                    const float* pos, float* out, int B, int C, int H, int W, int ph, int pw, int d, int regs) {
+    TL_NOTNULL(ctx); TL_NOTNULL(proj_t); TL_NOTNULL(cls_reg); TL_NOTNULL(pos); TL_NOTNULL(out);
+    TL_REQUIRE(prec_ok(prec), "unknown precision %d", prec);
+    TL_TRY(check_vit_image(B, C, H, W, ph, pw, d, regs));
+    if (B == 0) return TLNN_OK;
+    TL_NOTNULL(img);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    const long long M = (long long)B * (H / ph) * (W / pw);
+    TL_TRY(tl_ws_reserve(ctx, vit_project_ws_bytes(prec, M, d, ph * pw * C)));
+    return vit_project_enqueue(ctx, prec, img, proj_t, cls_reg, pos, out, B, C, H, W, ph, pw, d, regs, tl_ws_cursor(ctx));
+}
+
 extern "C" int tlnn_vit_head_fwd(tlnn_ctx* ctx, int prec, const float* x, const void* w_t, const float* bias, float* out,
                                  int B, int T, int d, int n_out) {
     TL_NOTNULL(ctx); TL_NOTNULL(w_t); TL_NOTNULL(out);
@@ -336,6 +357,14 @@ extern "C" int tlnn_vit_head_fwd(tlnn_ctx* ctx, int prec, const float* x, const 
 
 namespace {
 
+// Launches made inside the scope may carry the programmatic-dependent-launch attribute (honoured by the kernels that
+// begin with a grid-dependency wait; the others are launched plainly and serialise as usual).
+struct pdl_scope {
+    tlnn_ctx* c; bool old;
+    pdl_scope(tlnn_ctx* cc, bool on) : c(cc), old(cc->pdl) { c->pdl = on; }
+    ~pdl_scope() { c->pdl = old; }
+};
+
 // Everything tlnn_gpt_prefill enqueues, given that the workspace is already reserved.
 int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T, float* logits,
                     int32_t* tokens) {
@@ -343,11 +372,7 @@ int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int
     // Kernels that begin with a grid-dependency wait (LayerNorm, the one-CTA GEMM, the arg-max reduction) may be launched
     // while their predecessor still runs; the others are launched plainly and serialise as usual.  TLNN_PDL_PREFILL=1.
     static const bool pdl_allowed = getenv("TLNN_PDL_PREFILL") && strcmp(getenv("TLNN_PDL_PREFILL"), "1") == 0;
-    struct pdl_scope {
-        tlnn_ctx* c; bool old;
-        pdl_scope(tlnn_ctx* cc, bool on) : c(cc), old(cc->pdl) { c->pdl = on; }
-        ~pdl_scope() { c->pdl = old; }
-    } scope(ctx, pdl_allowed && !ctx->prof_classes);
+    pdl_scope scope(ctx, pdl_allowed && !ctx->prof_classes);
     const int d = m->d;
     const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
     const size_t tail = block_ws_bytes(m->prec, M, d);
@@ -370,27 +395,27 @@ int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int
     return run_head(ctx, m->prec, a, m->head_t, m->head_bias, logits, tokens, M, d, m->vocab, cur);
 }
 
-// A repeated call (same model description, buffers and shape) replays a captured CUDA graph of the first repetition:
-// a step of a small shard is 172 kernels of tens of microseconds, and the gaps between plain launches add up.
+// A repeated whole-model call (same model description, buffers and shape) replays a captured CUDA graph of the first
+// repetition: a step of a small shard is a hundred or more kernels of tens of microseconds, and the gaps between plain
+// launches add up.  The context keeps one such graph, keyed by the bytes of everything the enqueued work depends on.
 // TLNN_PREFILL_GRAPH=0 switches this off; per-class profiling always uses plain launches.
-struct prefill_cache {
-    tlnn_gpt_model m;
-    std::vector<tlnn_block_params> blocks;
-    const void* ids = nullptr;
-    int ids_type = 0, B = 0, T = 0;
-    float* logits = nullptr;
-    int32_t* tokens = nullptr;
-    char* ws = nullptr;
+struct replay_cache {
+    std::vector<unsigned char> key;
     int seen = 0;                       // identical calls so far
     long long launches = 0;             // kernels per replay
     cudaGraphExec_t exec = nullptr;
+};
 
-    bool matches(const tlnn_ctx* ctx, const tlnn_gpt_model* mm, const void* i, int it, int b, int t, float* lg, int32_t* tk) const {
-        if (ids != i || ids_type != it || B != b || T != t || logits != lg || tokens != tk || ws != ctx->ws) return false;
-        tlnn_gpt_model x = *mm, y = m;
-        x.blocks = nullptr; y.blocks = nullptr;
-        if (memcmp(&x, &y, sizeof(x)) != 0 || (int)blocks.size() != mm->layers) return false;
-        return mm->layers == 0 || memcmp(blocks.data(), mm->blocks, sizeof(tlnn_block_params) * blocks.size()) == 0;
+struct replay_key {
+    std::vector<unsigned char> bytes;
+    template <typename V> replay_key& add(const V& v) {
+        const unsigned char* p = reinterpret_cast<const unsigned char*>(&v);
+        bytes.insert(bytes.end(), p, p + sizeof(V));
+        return *this;
+    }
+    replay_key& add_block(const tlnn_block_params& b) {
+        return add(b.ln1_gamma).add(b.ln1_beta).add(b.wqkv_t).add(b.bqkv).add(b.wo_t).add(b.bo).add(b.ln2_gamma).add(b.ln2_beta)
+              .add(b.w1_t).add(b.b1).add(b.w2_t).add(b.b2);
     }
 };
 
@@ -403,10 +428,79 @@ bool prefill_graph_enabled() {
     return on == 1;
 }
 
+// Runs `enqueue` (which launches on ctx->stream and returns a status): plainly the first time a key is seen, as a stream
+// capture that is instantiated and launched the second time, as a replay of that graph from then on.
+template <typename F>
+int replay_or_run(tlnn_ctx* ctx, const replay_key& key, F&& enqueue) {
+    if (!prefill_graph_enabled() || ctx->prof_classes) return enqueue();
+    replay_cache* c = static_cast<replay_cache*>(ctx->prefill_cache);
+    if (c && c->key == key.bytes) {
+        if (c->exec) {
+            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
+            ctx->launches += c->launches;
+            return TLNN_OK;
+        }
+        if (++c->seen == 2) {
+            const long long before = ctx->launches;
+            TL_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            const int st = enqueue();
+            cudaGraph_t g = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
+            c->launches = ctx->launches - before;
+            ctx->launches = before;
+            if (st != TLNN_OK) { if (g) cudaGraphDestroy(g); return st; }
+            if (ce != cudaSuccess) return tl_cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
+            const cudaError_t ie = cudaGraphInstantiate(&c->exec, g, 0);
+            cudaGraphDestroy(g);
+            if (ie != cudaSuccess) { c->exec = nullptr; return tl_cuda_fail(ie, "cudaGraphInstantiate", __FILE__, __LINE__); }
+            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
+            ctx->launches += c->launches;
+            return TLNN_OK;
+        }
+        return enqueue();
+    }
+    // a new description: remember it, run it with plain launches
+    tl_prefill_cache_free(ctx);
+    c = new replay_cache();
+    c->key = key.bytes;
+    c->seen = 1;
+    ctx->prefill_cache = c;
+    return enqueue();
+}
+
+// Everything tlnn_vit_forward enqueues, given that the workspace is already reserved.
+int vit_forward_enqueue(tlnn_ctx* ctx, const tlnn_vit_model* m, const float* img, int B, float* out) {
+    static const bool pdl_off = getenv("TLNN_PDL_VIT") && strcmp(getenv("TLNN_PDL_VIT"), "0") == 0;
+    pdl_scope scope(ctx, !pdl_off && !ctx->prof_classes);
+    const int d = m->d, n_patch = (m->height / m->patch_h) * (m->width / m->patch_w), T = 1 + m->registers + n_patch;
+    const long long M = (long long)B * T;
+    tl_ws_cursor cur(ctx);
+    float* xa = cur.take<float>((size_t)M * d);
+    float* xb = cur.take<float>((size_t)M * d);
+    TL_TRY(vit_project_enqueue(ctx, m->prec, img, m->proj_t, m->cls_reg, m->pos, xa, B, m->channels, m->height, m->width,
+                               m->patch_h, m->patch_w, d, m->registers, cur));
+    for (int l = 0; l < m->layers; l++) {
+        if (m->prec == TLNN_PREC_BF16) {
+            TL_TRY(run_block(ctx, m->prec, xa, &m->blocks[l], m->act, xa, B, T, d, m->heads, 0, cur));     // in place
+        } else {
+            TL_TRY(run_block(ctx, m->prec, xa, &m->blocks[l], m->act, xb, B, T, d, m->heads, 0, cur));
+            float* t = xa; xa = xb; xb = t;
+        }
+    }
+    // LayerNorm works row by row and the head reads the class row only: normalise that row of every image
+    float* cls = cur.take<float>((size_t)B * d);
+    void* a = cur.take<char>((size_t)B * d * op_size(m->prec));
+    TL_TRY(tl_convert(ctx, xa, (long long)T * d, cls, TL_OUT_F32, B, d));
+    TL_TRY(tl_layernorm(ctx, cls, m->lnf_gamma, m->lnf_beta, 1e-5f, a, op_kind(m->prec), B, d));
+    tl_gemm_epilogue e;
+    e.bias = m->head_bias; e.out = out; e.ldo = m->n_out; e.out_kind = TL_OUT_F32;
+    return tl_gemm(ctx, m->prec, a, d, m->head_t, d, B, m->n_out, d, e);
+}
+
 }  // namespace
 
 void tl_prefill_cache_free(tlnn_ctx* ctx) {
-    prefill_cache* c = static_cast<prefill_cache*>(ctx->prefill_cache);
+    replay_cache* c = static_cast<replay_cache*>(ctx->prefill_cache);
     if (!c) return;
     if (c->exec) cudaGraphExecDestroy(c->exec);
     delete c;
@@ -435,42 +529,42 @@ extern "C" int tlnn_gpt_prefill(tlnn_ctx* ctx, const tlnn_gpt_model* m, const vo
         const size_t head = head_ws_bytes(ctx, m->prec, M, d, m->vocab, tokens != nullptr);
         TL_TRY(tl_ws_reserve(ctx, 2 * stream_bytes + (tail > head ? tail : head)));
     }
-    if (!prefill_graph_enabled() || ctx->prof_classes) return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+    replay_key key;
+    key.add('G').add(m->vocab).add(m->context).add(m->d).add(m->heads).add(m->layers).add(m->act).add(m->prec)
+       .add(m->tok_table).add(m->pos_table).add(m->lnf_gamma).add(m->lnf_beta).add(m->head_t).add(m->head_bias)
+       .add(ids).add(ids_type).add(B).add(T).add(logits).add(tokens).add(ctx->ws);
+    for (int l = 0; l < m->layers; l++) key.add_block(m->blocks[l]);
+    return replay_or_run(ctx, key, [&] { return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens); });
+}
 
-    prefill_cache* c = static_cast<prefill_cache*>(ctx->prefill_cache);
-    if (c && c->matches(ctx, m, ids, ids_type, B, T, logits, tokens)) {
-        if (c->exec) {
-            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
-            ctx->launches += c->launches;
-            return TLNN_OK;
-        }
-        if (++c->seen == 2) {
-            // second identical call: capture it, then run the capture
-            const long long before = ctx->launches;
-            TL_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-            const int st = prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
-            cudaGraph_t g = nullptr;
-            const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
-            c->launches = ctx->launches - before;
-            ctx->launches = before;
-            if (st != TLNN_OK) { if (g) cudaGraphDestroy(g); return st; }
-            if (ce != cudaSuccess) return tl_cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
-            const cudaError_t ie = cudaGraphInstantiate(&c->exec, g, 0);
-            cudaGraphDestroy(g);
-            if (ie != cudaSuccess) { c->exec = nullptr; return tl_cuda_fail(ie, "cudaGraphInstantiate", __FILE__, __LINE__); }
-            TL_CUDA(cudaGraphLaunch(c->exec, ctx->stream));
-            ctx->launches += c->launches;
-            return TLNN_OK;
-        }
-        return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+extern "C" int tlnn_vit_forward(tlnn_ctx* ctx, const tlnn_vit_model* m, const float* img, int B, float* out) {
+    TL_NOTNULL(ctx); TL_NOTNULL(m); TL_NOTNULL(m->proj_t); TL_NOTNULL(m->cls_reg); TL_NOTNULL(m->pos); TL_NOTNULL(m->blocks);
+    TL_NOTNULL(m->lnf_gamma); TL_NOTNULL(m->lnf_beta); TL_NOTNULL(m->head_t); TL_NOTNULL(out);
+    TL_REQUIRE(prec_ok(m->prec), "unknown precision %d", m->prec);
+    TL_REQUIRE(m->layers >= 0 && m->n_out > 0, "vit_forward: bad model description");
+    TL_REQUIRE(m->act >= TLNN_ACT_NONE && m->act <= TLNN_ACT_RELU, "unknown activation %d", m->act);
+    TL_TRY(check_vit_image(B, m->channels, m->height, m->width, m->patch_h, m->patch_w, m->d, m->registers));
+    const int n_patch = (m->height / m->patch_h) * (m->width / m->patch_w), T = 1 + m->registers + n_patch;
+    TL_TRY(check_block_shape(B, T, m->d, m->heads));
+    for (int l = 0; l < m->layers; l++) TL_TRY(check_block_params(&m->blocks[l]));
+    if (B == 0) return TLNN_OK;
+    TL_NOTNULL(img);
+    TL_CUDA(cudaSetDevice(ctx->device));
+    const long long M = (long long)B * T;
+    const int d = m->d;
+    {
+        const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
+        const size_t proj = vit_project_ws_bytes(m->prec, (long long)B * n_patch, d, m->patch_h * m->patch_w * m->channels);
+        const size_t tail = block_ws_bytes(m->prec, M, d);
+        const size_t head = tl_ws_round((size_t)B * d * 4) + tl_ws_round((size_t)B * d * op_size(m->prec));
+        size_t most = proj > tail ? proj : tail;
+        if (head > most) most = head;
+        TL_TRY(tl_ws_reserve(ctx, 2 * stream_bytes + most));
     }
-    // a new description: remember it, run it with plain launches
-    tl_prefill_cache_free(ctx);
-    c = new prefill_cache();
-    c->m = *m;
-    c->blocks.assign(m->blocks, m->blocks + m->layers);
-    c->ids = ids; c->ids_type = ids_type; c->B = B; c->T = T; c->logits = logits; c->tokens = tokens; c->ws = ctx->ws;
-    c->seen = 1;
-    ctx->prefill_cache = c;
-    return prefill_enqueue(ctx, m, ids, ids_type, B, T, logits, tokens);
+    replay_key key;
+    key.add('V').add(m->channels).add(m->height).add(m->width).add(m->patch_h).add(m->patch_w).add(m->d).add(m->heads)
+       .add(m->layers).add(m->act).add(m->prec).add(m->registers).add(m->n_out).add(m->proj_t).add(m->cls_reg).add(m->pos)
+       .add(m->lnf_gamma).add(m->lnf_beta).add(m->head_t).add(m->head_bias).add(img).add(B).add(out).add(ctx->ws);
+    for (int l = 0; l < m->layers; l++) key.add_block(m->blocks[l]);
+    return replay_or_run(ctx, key, [&] { return vit_forward_enqueue(ctx, m, img, B, out); });
 }

@@ -26,7 +26,7 @@ from .utils import Layer
 from .layers import *  # noqa: F401,F403
 from .layers import Dropout, LayerNorm, TransformerBlock, Dense
 from .transformer_adapters import *  # noqa: F401,F403
-from .transformer_adapters import GPTEmbedFront, GPTEmbedBack, _ids_code
+from .transformer_adapters import GPTEmbedFront, GPTEmbedBack, VitProjector, VitMLPHead, _ids_code
 
 
 class GPTPlan:
@@ -75,6 +75,47 @@ class GPTPlan:
                           backend.precision_code(), f.embedding_table.table.ptr, f.pos_embedding_table.ptr,
                           arr, self.final_norm.gamma.ptr, self.final_norm.beta.ptr, head_t, head_b)
         return m, arr, V
+
+
+class ViTPlan:
+    """The tlnn_vit_model description of a layer list that follows the ViT recipe (VitProjector, [Dropout], encoder
+    TransformerBlocks, LayerNorm, VitMLPHead)."""
+
+    def __init__(self, front, blocks, final_norm, head):
+        self.front, self.blocks, self.final_norm, self.head = front, blocks, final_norm, head
+
+    @staticmethod
+    def match(layers):
+        ls = [l for l in layers if not isinstance(l, Dropout)]
+        if len(ls) < 3 or not isinstance(ls[0], VitProjector) or not isinstance(ls[-2], LayerNorm):
+            return None
+        if not isinstance(ls[-1], VitMLPHead):
+            return None
+        blocks = ls[1:-2]
+        if not all(isinstance(b, TransformerBlock) and not b.attn_block.is_decoder for b in blocks):
+            return None
+        d = ls[0].embedding_dim
+        if blocks and {(b.attn_block.embedding_dim, b.attn_block.num_heads, b.ffn.act_code()) for b in blocks} != \
+                {(d, blocks[0].attn_block.num_heads, blocks[0].ffn.act_code())}:
+            return None
+        if ls[-1].weights.shape[0] != d or ls[-2].gamma.shape[-1] != d:
+            return None
+        return ViTPlan(ls[0], blocks, ls[-2], ls[-1])
+
+    def model(self):
+        """Build the C struct; the returned tuple keeps the block array alive."""
+        f = self.front
+        arr = (_lib.BlockParams * max(len(self.blocks), 1))()
+        for i, b in enumerate(self.blocks):
+            arr[i] = b.block_params()
+        heads = self.blocks[0].attn_block.num_heads if self.blocks else 1
+        act = self.blocks[0].ffn.act_code() if self.blocks else _lib.ACT_NONE
+        n_out = self.head.weights.shape[1]
+        m = _lib.ViTModel(f.channels, f.height, f.width, f.patch_size[0], f.patch_size[1], f.embedding_dim, heads,
+                          len(self.blocks), act, backend.precision_code(), f.cls_reg_size - 1, n_out,
+                          f._proj.ptr(), f.cls_reg_tokens.ptr, f.positional_embeddings.ptr, arr,
+                          self.final_norm.gamma.ptr, self.final_norm.beta.ptr, self.head._w.ptr(), self.head.bias.ptr)
+        return m, arr, n_out
 
 
 def _rows(x, lo, hi):
@@ -137,13 +178,25 @@ class Network:
                 raise NotImplementedError("dropout masks are training behaviour; call set_eval(True) first")
 
     def predict_logits(self, input, comm=None):
-        """Same result as ``predict`` for the GPT recipe, as one fused library call (no per-layer outputs kept).
+        """Same result as ``predict`` for the GPT and the ViT recipes, as one fused library call (no per-layer outputs
+        kept; a repeated call on the same buffers replays a captured CUDA graph).
         With ``comm`` every rank runs its slice of the batch rows and the logits are all-gathered (see
         ``predict_tokens``); for large vocabularies prefer gathering tokens."""
         if comm is not None and comm.world > 1:
             from .comm import sharded_rows
             return sharded_rows(comm, len(input), lambda lo, hi: self.predict_logits(_rows(input, lo, hi)),
                                 comm.allgather_logits)
+        vit = ViTPlan.match(self.layers)
+        if vit is not None:
+            self._check_eval()
+            img = as_device(input, np.float32)
+            want = (vit.front.channels, vit.front.height, vit.front.width)
+            if img.ndim != 4 or img.shape[1:] != want:
+                raise ValueError(f"cannot reshape array of shape {img.shape} into patches of a {want} image")
+            m, keep, n_out = vit.model()
+            scores = DeviceArray((img.shape[0], n_out), np.float32)
+            check(lib.tlnn_vit_forward(backend.ctx(), C.byref(m), img.ptr, img.shape[0], scores.ptr))
+            return scores
         plan = GPTPlan.match(self.layers)
         if plan is None:
             return self.predict(input)
@@ -178,7 +231,7 @@ class Network:
             tokens = DeviceArray((B, T), np.int32)
             check(lib.tlnn_gpt_prefill(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), B, T, None, tokens.ptr))
             return tokens
-        return argmax_last(self.predict(input))
+        return argmax_last(self.predict_logits(input))
 
     def evaluate(self, test_data, test_labels, criterion=None, batch_size=64, prefetch=True):
         """network.py:145-160: mean cross-entropy and accuracy of ``predict`` over ``test_data`` in batches.  The
