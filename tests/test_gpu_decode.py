@@ -151,3 +151,43 @@ def test_decode_c4_full_size(engine, c4):
         differ = out[rows, 128:] != a[:, 127:]
         excused = (top - second)[:, 127:] < tol
         assert not (differ & ~excused).any(), f"{int((differ & ~excused).sum())} decode tokens differ from prefill on a clear arg-max"
+
+
+def test_decode_cache_longer_than_the_default_shared_memory(engine):
+    """The single-query attention kernel keeps one float32 score per cached position in shared memory: a cache of
+    16000 positions needs 64 KB (above the 48 KB a kernel gets without asking), one of 60000 positions does not fit an
+    SM and is refused before anything is launched."""
+    import ctypes as C
+    from torchless_nn_b200 import backend
+    from torchless_nn_b200._lib import lib, check
+    from torchless_nn_b200.activations import GeLU
+    from torchless_nn_b200.device_array import DeviceArray, as_token_ids
+    from torchless_nn_b200.layers import TransformerBlock, LayerNorm
+    from torchless_nn_b200.network import Network, GPTPlan
+    from torchless_nn_b200.transformer_adapters import GPTEmbeddingTable, GPTEmbedFront, GPTEmbedBack, _ids_code
+    for precision in ("tf32", "bf16"):
+        engine.set_precision(precision)
+        try:
+            table = GPTEmbeddingTable(50, 64)
+            net = Network([GPTEmbedFront(table, 70000), TransformerBlock(64, 70000, 2, GeLU, decoder=True),
+                           LayerNorm(64), GPTEmbedBack(table)])
+            net.set_eval(True)
+            prompts = np.random.default_rng(5).integers(0, 50, (3, 9)).astype(np.int32)
+            want = net.generate_greedy(prompts, 6).get()[:, 9:]              # cache of 15 positions
+            m, keep, V = GPTPlan.match(net.layers).model()
+            ids = as_token_ids(prompts)
+
+            def run(max_len):
+                first, rest, dec = DeviceArray((3,), np.int32), DeviceArray((3, 5), np.int32), C.c_void_p()
+                check(lib.tlnn_decode_begin(backend.ctx(), C.byref(m), ids.ptr, _ids_code(ids), 3, 9, max_len, first.ptr, C.byref(dec)))
+                try:
+                    check(lib.tlnn_decode_run(dec, first.ptr, 5, rest.ptr))
+                    return np.concatenate([first.get()[:, None], rest.get()], axis=1)
+                finally:
+                    lib.tlnn_decode_end(dec)
+
+            assert np.array_equal(run(16000), want)
+            with pytest.raises(ValueError, match="shared memory"):
+                run(60000)
+        finally:
+            engine.set_precision("tf32")
