@@ -68,8 +68,7 @@ __global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const fl
 template <typename E, int HD>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, E* __restrict__ out,
-                        const int* __restrict__ len_ptr, int H, int cache_len, float inv_sqrt_hd, int round_out,
-                        const E* __restrict__ ahead_k, const E* __restrict__ ahead_v, int ahead_extra) {
+                        const int* __restrict__ len_ptr, int H, int cache_len, float inv_sqrt_hd, int round_out) {
     constexpr int PER = 16 / sizeof(E);            // elements per 16-byte load
     constexpr int TPR = HD / PER;                  // threads per key row
     constexpr int KPP = 128 / TPR;                 // keys per pass
@@ -87,20 +86,6 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
     E* vbase = vc + ((long long)b * cache_len) * d + h * HD;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = tid % TPR, grp = tid / TPR;    // 16-byte unit inside the row, key residue
-    // Ask for the cache rows the next attention launch will read (the next layer's, or layer 0's for the next token) to
-    // be brought into L2 while the products in between run: a step is latency-bound, and those 4 d^2 products leave
-    // HBM idle.  CTA (b, h) requests share h of sequence b's rows, keys and values; a request is fire-and-forget.
-    if (ahead_k != nullptr && tid == 96) {
-        const int rows = pos + ahead_extra;
-        const int r0 = (int)((long long)rows * h / H), r1 = (int)((long long)rows * (h + 1) / H);
-        const size_t off0 = ((size_t)b * cache_len + r0) * d * sizeof(E);
-        const size_t bytes = (size_t)(r1 - r0) * d * sizeof(E);
-        for (size_t off = 0; off < bytes; off += 65536) {
-            const unsigned nb = (unsigned)(bytes - off < 65536 ? bytes - off : 65536);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char*>(ahead_k) + off0 + off), "r"(nb) : "memory");
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char*>(ahead_v) + off0 + off), "r"(nb) : "memory");
-        }
-    }
     // this thread's slice of the query, and the append of the new row (first TPR threads, 16 bytes each)
     float q[PER];
     {
@@ -253,17 +238,10 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
     const float inv = 1.f / sqrtf((float)hd);
     const size_t smem = (size_t)dec->max_len * sizeof(float);
     const int round_out = dec->m.prec == TLNN_PREC_TF32;
-    // the launch after this one reads the next layer's cache, or layer 0's with one more row (the next token's step)
-    static const bool ahead_on = !(getenv("TLNN_DECODE_PREFETCH") && strcmp(getenv("TLNN_DECODE_PREFETCH"), "0") == 0);
-    const bool last = layer + 1 == dec->m.layers;
-    const size_t ahead_off = ahead_on ? (last ? 0 : (size_t)(layer + 1) * layer_elems) : 0;
-    const int ahead_extra = last ? 1 : 0;
 #define DA_CASE(E, HDV)                                                                                              \
     TL_LAUNCH(ctx, "decode_attention", tl_launch_kernel(ctx, decode_attention_kernel<E, HDV>, dim3(B * H), dim3(128), smem, \
                   (const E*)dec->qkv, (E*)dec->kcache + layer * layer_elems, (E*)dec->vcache + layer * layer_elems, \
-                  (E*)dec->att, dec->d_len, H, dec->max_len, inv, round_out,                                         \
-                  ahead_on ? (const E*)dec->kcache + ahead_off : (const E*)nullptr,                                  \
-                  ahead_on ? (const E*)dec->vcache + ahead_off : (const E*)nullptr, ahead_extra))
+                  (E*)dec->att, dec->d_len, H, dec->max_len, inv, round_out))
     if (dec->m.prec == TLNN_PREC_BF16) {
         if (hd == 32) DA_CASE(__nv_bfloat16, 32);
         else if (hd == 64) DA_CASE(__nv_bfloat16, 64);

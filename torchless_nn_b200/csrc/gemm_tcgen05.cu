@@ -596,6 +596,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    tl_grid_dependency_trigger();            // the successor may start launching; it waits for this grid itself
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -629,6 +630,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     cluster_sync_all();                       // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers, TMEM and descriptors are ready; nothing below may touch global memory before the predecessor is done
+    tl_grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
@@ -768,16 +771,18 @@ int launch_pair(tlnn_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
     const long long total = (long long)m_pairs * n_tiles;
     TL_REQUIRE(total < (1ll << 31), "gemm: too many tiles");
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // see tl_launch_kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = PairCfg::SMEM;
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->pdl ? 2 : 1;
     static int max_clusters = 0;
     if (max_clusters == 0) {
         TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM));
