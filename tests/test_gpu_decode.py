@@ -153,10 +153,9 @@ def test_decode_c4_full_size(engine, c4):
         assert not (differ & ~excused).any(), f"{int((differ & ~excused).sum())} decode tokens differ from prefill on a clear arg-max"
 
 
-def test_decode_cache_longer_than_the_default_shared_memory(engine):
-    """The single-query attention kernel keeps one float32 score per cached position in shared memory: a cache of
-    16000 positions needs 64 KB (above the 48 KB a kernel gets without asking), one of 60000 positions does not fit an
-    SM and is refused before anything is launched."""
+def test_decode_with_a_long_cache(engine):
+    """The single-query attention keeps nothing per cached position in shared memory (one pass, online softmax), so the
+    cache length is bounded by the context only: caches of 16000 and 60000 positions give the tokens of a short one."""
     import ctypes as C
     from torchless_nn_b200 import backend
     from torchless_nn_b200._lib import lib, check
@@ -187,7 +186,6 @@ def test_decode_cache_longer_than_the_default_shared_memory(engine):
                     lib.tlnn_decode_end(dec)
 
             assert np.array_equal(run(16000), want)
-            with pytest.raises(ValueError, match="shared memory"):
-                run(60000)
+            assert np.array_equal(run(60000), want)
         finally:
             engine.set_precision("tf32")

@@ -207,6 +207,8 @@ int tl_gemm(tlnn_ctx* ctx, int prec, const void* a, long long lda, const void* w
 // Tile width the GEMM will pick for this problem, and the number of arg-max candidates it leaves per row
 // (the partial buffer holds rows x tl_gemm_argmax_parts float2 entries).
 int tl_gemm_bn(int M, int N, int sm_count);
+// Whether tl_gemm runs this product on the CTA-pair kernel (256 x 256 tiles) rather than the one-CTA kernel.
+bool tl_gemm_uses_pair(int prec, int M, int N, int sm_count);
 int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count);
 
 // Fused attention on a packed projection buffer: qkv is (B, T, 3d) with columns [0,d) Q, [d,2d) K, [2d,3d) V
@@ -219,8 +221,9 @@ int tl_attention_core(tlnn_ctx* ctx, int prec, const void* qkv, void* out, int o
 bool tl_attention_tf32_applies(int T, int hd);
 int tl_attention_tf32(tlnn_ctx* ctx, const float* qkv, float* out, int B, int T, int heads, int causal, int round_out);
 
-// Copy the K and V thirds of a packed (B*T, 3d) projection into per-layer caches laid out (B, cache_len, d).
-int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int cache_len);
+// Copy the K and V thirds of a packed (B*T, 3d) projection into per-layer caches laid out (B, heads, cache_len, d / heads):
+// the rows of one (sequence, head) are contiguous, which is how the single-query attention of a decode step reads them.
+int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int heads, int cache_len);
 int tl_run_block_kv(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* p, int act, float* out, int B, int T,
                     int d, int heads, char* ws_base, void* kcache, void* vcache, int cache_len);
 size_t tl_block_ws_bytes(int prec, long long M, int d);

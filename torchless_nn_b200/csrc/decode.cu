@@ -32,15 +32,17 @@ __device__ __forceinline__ float round_tf32(float x) {
 // qkv (B*T, 3d) -> kcache / vcache (B, cache_len, d), rows [0, T)
 template <typename E>
 __global__ void kv_store_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, int B, int T, int d,
-                                int cache_len) {
+                                int hd, int cache_len) {
     const long long total = (long long)B * T * d;
     const long long stride = (long long)gridDim.x * blockDim.x;
+    const int H = d / hd;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int c = (int)(i % d);
         const long long row = i / d;
         const int t = (int)(row % T);
         const long long b = row / T;
-        const long long dst = (b * cache_len + t) * d + c;
+        const int h = c / hd;
+        const long long dst = ((b * H + h) * cache_len + t) * hd + (c - h * hd);
         kc[dst] = qkv[row * 3 * d + d + c];
         vc[dst] = qkv[row * 3 * d + 2 * d + c];
     }
@@ -62,29 +64,33 @@ __global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const fl
 }
 
 // Append the new row's K, V (from the packed (B, 3d) projection) at position *len, then attend the row's query over
-// cache rows [0, *len].  One CTA per (sequence, head).  Both passes read the cache with 16-byte loads: a group of
-// HD*sizeof(E)/16 threads covers one key row, and the 128 threads cover 128 / group keys per pass, so every pass keeps
-// many independent loads in flight.
+// cache rows [0, *len].  One CTA per (sequence, head); a group of HD*sizeof(E)/16 threads covers one key row with
+// 16-byte loads and the DA_THREADS threads cover DA_THREADS / group keys at a time.  One pass over the cache: a thread
+// requests the key rows AND the value rows of four keys before it uses the first, and every group keeps its own running
+// maximum, sum and weighted row (online softmax); the groups are merged through shared memory at the end.  The kernel
+// is a chain of round trips to L2 / HBM, so its time is the number of such rounds: the two-pass form (all scores, then
+// the maximum, then the values) needs twice as many and a score buffer as long as the cache.
+constexpr int DA_THREADS = 128;
 template <typename E, int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(DA_THREADS)
 decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, E* __restrict__ out,
                         const int* __restrict__ len_ptr, int H, int cache_len, float inv_sqrt_hd, int round_out) {
     constexpr int PER = 16 / sizeof(E);            // elements per 16-byte load
     constexpr int TPR = HD / PER;                  // threads per key row
-    constexpr int KPP = 128 / TPR;                 // keys per pass
-    extern __shared__ float sm[];
-    float* sc = sm;                                // cache_len scores / probabilities
-    __shared__ float red[8];
-    __shared__ float part[128 * PER];              // KPP x HD partial outputs
-    tl_grid_dependency_sync();
+    constexpr int KPP = DA_THREADS / TPR;          // keys per round of one load each
+    constexpr int UN = 4;                          // keys per thread and round
+    __shared__ float gm[KPP], gl[KPP];             // per group: running maximum (scaled scores) and sum
+    __shared__ float part[DA_THREADS * PER];       // KPP x HD weighted rows
     const int d = H * HD;
     const int b = blockIdx.x / H, h = blockIdx.x % H;
+    // a layer's cache is laid out (sequence, head, position, HD): the rows one CTA reads are contiguous in memory
+    E* kbase = kc + ((long long)(b * H + h) * cache_len) * HD;
+    E* vbase = vc + ((long long)(b * H + h) * cache_len) * HD;
+    const int tid = threadIdx.x;
+    tl_grid_dependency_sync();
     const int pos = *len_ptr;
     const int n = pos + 1;
     const E* row = qkv + (long long)b * 3 * d;
-    E* kbase = kc + ((long long)b * cache_len) * d + h * HD;
-    E* vbase = vc + ((long long)b * cache_len) * d + h * HD;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = tid % TPR, grp = tid / TPR;    // 16-byte unit inside the row, key residue
     // this thread's slice of the query, and the append of the new row (first TPR threads, 16 bytes each)
     float q[PER];
@@ -94,65 +100,76 @@ decode_attention_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __rest
 #pragma unroll
         for (int i = 0; i < PER; i++) q[i] = to_f<E>(e[i]);
         if (grp == 0) {
-            *reinterpret_cast<uint4*>(kbase + (long long)pos * d + sub * PER) = *reinterpret_cast<const uint4*>(row + d + h * HD + sub * PER);
-            *reinterpret_cast<uint4*>(vbase + (long long)pos * d + sub * PER) = *reinterpret_cast<const uint4*>(row + 2 * d + h * HD + sub * PER);
+            *reinterpret_cast<uint4*>(kbase + (long long)pos * HD + sub * PER) = *reinterpret_cast<const uint4*>(row + d + h * HD + sub * PER);
+            *reinterpret_cast<uint4*>(vbase + (long long)pos * HD + sub * PER) = *reinterpret_cast<const uint4*>(row + 2 * d + h * HD + sub * PER);
         }
     }
     __syncthreads();
-    // scores: TPR threads per key, partial dot products combined by shuffles inside the group
-    float mx = -INFINITY;
-    for (int k0 = 0; k0 < n; k0 += KPP) {
-        const int k = k0 + grp;
-        float s = 0.f;
-        if (k < n) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(kbase + (long long)k * d + sub * PER);
-            const E* e = reinterpret_cast<const E*>(&raw);
-#pragma unroll
-            for (int i = 0; i < PER; i++) s = fmaf(q[i], to_f<E>(e[i]), s);
-        }
-#pragma unroll
-        for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        s *= inv_sqrt_hd;
-        if (k < n) {
-            if (sub == 0) sc[k] = s;
-            mx = fmaxf(mx, s);
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    float sum = 0.f;
-    for (int k = tid; k < n; k += 128) {
-        const float p = expf(sc[k] - mx);
-        sc[k] = p;
-        sum += p;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) red[4 + warp] = sum;
-    __syncthreads();
-    sum = (red[4] + red[5]) + (red[6] + red[7]);
-    // weighted sum: the same thread-to-row mapping, PER output dimensions per thread, keys strided by KPP
+    float m_run = -INFINITY, l_run = 0.f;
     float acc[PER];
 #pragma unroll
     for (int i = 0; i < PER; i++) acc[i] = 0.f;
-    for (int k = grp; k < n; k += KPP) {
-        const float p = sc[k];
-        const uint4 raw = *reinterpret_cast<const uint4*>(vbase + (long long)k * d + sub * PER);
-        const E* e = reinterpret_cast<const E*>(&raw);
+    for (int k0 = 0; k0 < n; k0 += KPP * UN) {
+        uint4 kr[UN], vr[UN];
 #pragma unroll
-        for (int i = 0; i < PER; i++) acc[i] = fmaf(p, to_f<E>(e[i]), acc[i]);
+        for (int u = 0; u < UN; u++) {
+            const int k = k0 + u * KPP + grp;
+            if (k < n) {
+                kr[u] = *reinterpret_cast<const uint4*>(kbase + (long long)k * HD + sub * PER);
+                vr[u] = *reinterpret_cast<const uint4*>(vbase + (long long)k * HD + sub * PER);
+            } else {
+                kr[u] = make_uint4(0u, 0u, 0u, 0u);
+                vr[u] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        // scores: partial dot products combined by shuffles inside the group (every thread of a group ends with the sum)
+        float sc[UN];
+        float mb = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int k = k0 + u * KPP + grp;
+            const E* e = reinterpret_cast<const E*>(&kr[u]);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; i++) s = fmaf(q[i], to_f<E>(e[i]), s);
+#pragma unroll
+            for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            sc[u] = k < n ? s * inv_sqrt_hd : -INFINITY;
+            mb = fmaxf(mb, sc[u]);
+        }
+        const float m_new = fmaxf(m_run, mb);
+        if (m_new > -INFINITY) {                   // the same for all threads of a group
+            const float alpha = __expf(m_run - m_new);          // 0 while m_run is still -inf
+            l_run *= alpha;
+#pragma unroll
+            for (int i = 0; i < PER; i++) acc[i] *= alpha;
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const float p = __expf(sc[u] - m_new);          // 0 for a key beyond the cache
+                l_run += p;
+                const E* e = reinterpret_cast<const E*>(&vr[u]);
+#pragma unroll
+                for (int i = 0; i < PER; i++) acc[i] = fmaf(p, to_f<E>(e[i]), acc[i]);
+            }
+            m_run = m_new;
+        }
     }
+    if (sub == 0) { gm[grp] = m_run; gl[grp] = l_run; }
 #pragma unroll
     for (int i = 0; i < PER; i++) part[(grp * TPR + sub) * PER + i] = acc[i];
     __syncthreads();
     if (tid < HD) {
-        float o = 0.f;
+        float mx = gm[0];
+#pragma unroll
+        for (int g = 1; g < KPP; g++) mx = fmaxf(mx, gm[g]);
+        float o = 0.f, den = 0.f;
 #pragma unroll 4
-        for (int g = 0; g < KPP; g++) o += part[g * HD + tid];
-        o /= sum;
+        for (int g = 0; g < KPP; g++) {
+            const float w = __expf(gm[g] - mx);               // 0 for a group that saw no key
+            den = fmaf(w, gl[g], den);
+            o = fmaf(w, part[g * HD + tid], o);
+        }
+        o /= den;
         if (round_out) o = round_tf32(o);
         out[(long long)b * d + h * HD + tid] = from_f<E>(o);
     }
@@ -185,17 +202,17 @@ inline int okind(int prec) { return prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OU
 
 }  // namespace
 
-int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int cache_len) {
+int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int heads, int cache_len) {
     const size_t n = (size_t)B * T * d;
     if (n == 0) return TLNN_OK;
     int grid = (int)((n + 255) / 256);
     if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
     if (prec == TLNN_PREC_BF16)
         TL_LAUNCH(ctx, "kv_store", kv_store_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>(
-                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, B, T, d, cache_len));
+                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, B, T, d, d / heads, cache_len));
     else
         TL_LAUNCH(ctx, "kv_store", kv_store_kernel<float><<<grid, 256, 0, ctx->stream>>>(
-                      (const float*)qkv, (float*)kcache, (float*)vcache, B, T, d, cache_len));
+                      (const float*)qkv, (float*)kcache, (float*)vcache, B, T, d, d / heads, cache_len));
     return TLNN_OK;
 }
 
@@ -236,10 +253,10 @@ int launch_decode_attention(tlnn_decoder* dec, int layer) {
     const int d = dec->m.d, H = dec->m.heads, hd = d / H, B = dec->B;
     const size_t layer_elems = (size_t)B * dec->max_len * d;
     const float inv = 1.f / sqrtf((float)hd);
-    const size_t smem = (size_t)dec->max_len * sizeof(float);
+    const size_t smem = 0;
     const int round_out = dec->m.prec == TLNN_PREC_TF32;
 #define DA_CASE(E, HDV)                                                                                              \
-    TL_LAUNCH(ctx, "decode_attention", tl_launch_kernel(ctx, decode_attention_kernel<E, HDV>, dim3(B * H), dim3(128), smem, \
+    TL_LAUNCH(ctx, "decode_attention", tl_launch_kernel(ctx, decode_attention_kernel<E, HDV>, dim3(B * H), dim3(DA_THREADS), smem, \
                   (const E*)dec->qkv, (E*)dec->kcache + layer * layer_elems, (E*)dec->vcache + layer * layer_elems, \
                   (E*)dec->att, dec->d_len, H, dec->max_len, inv, round_out))
     if (dec->m.prec == TLNN_PREC_BF16) {
@@ -354,27 +371,6 @@ extern "C" int tlnn_decode_begin(tlnn_ctx* ctx, const tlnn_gpt_model* m, const v
     TL_REQUIRE((long long)B * m->heads <= 65535, "decode: batch x heads exceeds 65535");
     TL_REQUIRE(ids_type == TLNN_I32 || ids_type == TLNN_I64 || ids_type == TLNN_U8, "token ids must be int32, int64 or uint8");
     TL_CUDA(cudaSetDevice(ctx->device));
-    {
-        // the single-query attention kernel keeps one float32 score per cached position in dynamic shared memory
-        const size_t score_bytes = (size_t)max_len * sizeof(float);
-        const void* fn = nullptr;
-        if (m->prec == TLNN_PREC_BF16) {
-            fn = hd == 32 ? (const void*)decode_attention_kernel<__nv_bfloat16, 32>
-               : hd == 64 ? (const void*)decode_attention_kernel<__nv_bfloat16, 64> : (const void*)decode_attention_kernel<__nv_bfloat16, 128>;
-        } else {
-            fn = hd == 32 ? (const void*)decode_attention_kernel<float, 32>
-               : hd == 64 ? (const void*)decode_attention_kernel<float, 64> : (const void*)decode_attention_kernel<float, 128>;
-        }
-        cudaFuncAttributes fa;
-        TL_CUDA(cudaFuncGetAttributes(&fa, fn));
-        int optin = 0;
-        TL_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device));
-        const long long room = (long long)optin - (long long)fa.sharedSizeBytes;
-        TL_REQUIRE((long long)score_bytes <= room, "decode: max_len %d needs %zu bytes of shared memory for the scores of one query; "
-                   "this GPU offers %lld (at most %lld positions)", max_len, score_bytes, room, room / 4);
-        if (score_bytes + fa.sharedSizeBytes > 48 * 1024)
-            TL_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)score_bytes));
-    }
 
     tlnn_decoder* dec = new tlnn_decoder();
     dec->ctx = ctx;

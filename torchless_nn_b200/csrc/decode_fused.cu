@@ -110,7 +110,7 @@ struct df_state {
     unsigned char* extras;    // attention: DF_NST slots of a unit's q, new-key and new-value rows
     uint64_t* att_full;       // [DF_NST] "stage filled" barriers of the attention ring
     long long att_count;      // chunks streamed through the attention ring so far (stage and parity continue across phases)
-    const CUtensorMap *kmap, *vmap;   // the key and value caches as (layers x sequences x positions, d) matrices
+    const CUtensorMap *kmap, *vmap;   // the key and value caches as (layers x sequences x heads x positions, head dimension) matrices
     volatile int* s_abort;    // shared: a wait of this CTA gave up
     int* s_bcast;             // shared: one int handed from thread 0 to the CTA
     const df_item* items;     // this CTA's items of one step
@@ -515,9 +515,9 @@ __device__ __noinline__ bool attention_phase(df_state& s, int layer, int pos) {
             uint64_t* bar = &s.att_full[st];
             sm100::fence_async_smem();
             sm100::mbar_expect_tx(bar, stage_bytes + (j_issue == 0 ? 3u * ROWB : 0u));
-            const int row0 = (layer * p.B + b) * p.max_len + j_issue * CK;
-            sm100::tma_load_2d(ring + st * stage_bytes, s.kmap, sm100::smem_u32(bar), h * HD, row0);
-            sm100::tma_load_2d(ring + st * stage_bytes + (uint32_t)CK * ROWB, s.vmap, sm100::smem_u32(bar), h * HD, row0);
+            const int row0 = ((layer * p.B + b) * H + h) * p.max_len + j_issue * CK;
+            sm100::tma_load_2d(ring + st * stage_bytes, s.kmap, sm100::smem_u32(bar), 0, row0);
+            sm100::tma_load_2d(ring + st * stage_bytes + (uint32_t)CK * ROWB, s.vmap, sm100::smem_u32(bar), 0, row0);
             if (j_issue == 0) {
                 const bf16* row = p.qkv + (size_t)b * 3 * d + h * HD;
                 for (int which = 0; which < 3; which++)
@@ -636,8 +636,8 @@ __device__ __noinline__ bool attention_phase(df_state& s, int layer, int pos) {
                     for (int i = 0; i < 4; i++) ow[i] = pack_bf16(o8[2 * i] * rs, o8[2 * i + 1] * rs);
                     *reinterpret_cast<uint4*>(p.att + (size_t)b * d + h * HD + sub * 8) = o;
                     // append this step's key and value rows to the cache
-                    *reinterpret_cast<uint4*>(kcache + ((size_t)b * p.max_len + pos) * d + h * HD + sub * 8) = kn;
-                    *reinterpret_cast<uint4*>(vcache + ((size_t)b * p.max_len + pos) * d + h * HD + sub * 8) = vn;
+                    *reinterpret_cast<uint4*>(kcache + (((size_t)b * H + h) * p.max_len + pos) * HD + sub * 8) = kn;
+                    *reinterpret_cast<uint4*>(vcache + (((size_t)b * H + h) * p.max_len + pos) * HD + sub * 8) = vn;
                 }
             }
             m_run = -INFINITY;
@@ -662,11 +662,14 @@ __device__ __noinline__ bool attention_phase(df_state& s, int layer, int pos) {
 __device__ void prefetch_cache(const df_params& p, int layer, int pos) {
     if ((int)blockIdx.x >= 2 * p.B || threadIdx.x != 32 || pos <= 0) return;
     const int b = blockIdx.x >> 1;
-    const bf16* base = ((blockIdx.x & 1) ? p.vcache : p.kcache) + ((size_t)layer * p.B + b) * p.max_len * p.d;
-    const size_t bytes = (size_t)pos * p.d * 2;
-    for (size_t off = 0; off < bytes; off += 65536) {
-        const unsigned n = (unsigned)(bytes - off < 65536 ? bytes - off : 65536);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char*>(base) + off), "r"(n) : "memory");
+    const bf16* seq = ((blockIdx.x & 1) ? p.vcache : p.kcache) + ((size_t)layer * p.B + b) * p.max_len * p.d;
+    const size_t bytes = (size_t)pos * p.hd * 2;                   // the live rows of one head are contiguous
+    for (int h = 0; h < p.H; h++) {
+        const bf16* base = seq + (size_t)h * p.max_len * p.hd;
+        for (size_t off = 0; off < bytes; off += 65536) {
+            const unsigned n = (unsigned)(bytes - off < 65536 ? bytes - off : 65536);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char*>(base) + off), "r"(n) : "memory");
+        }
     }
 }
 
@@ -948,9 +951,9 @@ int tl_decode_fused_launch(tlnn_ctx* ctx, const tl_decode_fused_plan_t& plan, co
     TL_CUDA(cudaMemsetAsync(params.bar_flags, 0, 4096, ctx->stream));      // barrier flags (one word per CTA) and the abort flag
     df_params p = params;
     CUtensorMap kmap, vmap;
-    const long long cache_rows = (long long)p.L * p.B * p.max_len;
-    TL_TRY(sm100::make_plain_map(&kmap, p.kcache, cache_rows, p.d, p.d, p.hd, p.att_ck));
-    TL_TRY(sm100::make_plain_map(&vmap, p.vcache, cache_rows, p.d, p.d, p.hd, p.att_ck));
+    const long long cache_rows = (long long)p.L * p.B * p.H * p.max_len;
+    TL_TRY(sm100::make_plain_map(&kmap, p.kcache, cache_rows, p.hd, p.hd, p.hd, p.att_ck));
+    TL_TRY(sm100::make_plain_map(&vmap, p.vcache, cache_rows, p.hd, p.hd, p.hd, p.att_ck));
     static const bool want_prof = getenv("TLNN_DECODE_PROF") && strcmp(getenv("TLNN_DECODE_PROF"), "1") == 0;
     unsigned long long* d_prof = nullptr;
     if (want_prof) {

@@ -897,6 +897,7 @@ extern "C" int tlnn_selftest_wait(tlnn_ctx* ctx, int limit_ms) {
 }
 
 int tl_gemm_bn(int M, int N, int sm_count) { return pick_bn(M, N, sm_count); }
+bool tl_gemm_uses_pair(int prec, int M, int N, int sm_count) { return use_pair(sm_count, prec, M, N); }
 int tl_gemm_argmax_parts(int prec, int M, int N, int sm_count) {
     const int bn = use_pair(sm_count, prec, M, N) ? PairCfg::BN : pick_bn(M, N, sm_count);
     return 2 * ((N + bn - 1) / bn);     // two epilogue warps cover each row of a tile

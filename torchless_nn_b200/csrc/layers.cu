@@ -93,7 +93,7 @@ int run_block(tlnn_ctx* ctx, int prec, const float* x, const tlnn_block_params* 
     // the exact float32 attention kernels read unrounded q, k, v; the tensor-core one wants them rounded to TF32
     e1.out_kind = prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : (tl_attention_tf32_applies(T, d / heads) ? TL_OUT_TF32 : TL_OUT_F32);
     TL_TRY(tl_gemm(ctx, prec, a, d, p->wqkv_t, d, (int)M, 3 * d, d, e1));
-    if (kcache) TL_TRY(tl_kv_store(ctx, prec, qkv, kcache, vcache, B, T, d, cache_len));
+    if (kcache) TL_TRY(tl_kv_store(ctx, prec, qkv, kcache, vcache, B, T, d, heads, cache_len));
     TL_TRY(tl_attention_core(ctx, prec, qkv, att, kind, B, T, heads, d / heads, causal));
     tl_gemm_epilogue e2;
     e2.bias = p->bo; e2.residual = x; e2.ldr = d; e2.out = y; e2.ldo = d; e2.out_kind = TL_OUT_F32;
@@ -369,11 +369,15 @@ struct pdl_scope {
 int prefill_enqueue(tlnn_ctx* ctx, const tlnn_gpt_model* m, const void* ids, int ids_type, int B, int T, float* logits,
                     int32_t* tokens) {
     const long long M = (long long)B * T;
-    // Kernels that begin with a grid-dependency wait (LayerNorm, the one-CTA GEMM, the arg-max reduction) may be launched
-    // while their predecessor still runs; the others are launched plainly and serialise as usual.  TLNN_PDL_PREFILL=1.
-    static const bool pdl_allowed = getenv("TLNN_PDL_PREFILL") && strcmp(getenv("TLNN_PDL_PREFILL"), "1") == 0;
-    pdl_scope scope(ctx, pdl_allowed && !ctx->prof_classes);
+    // Kernels that begin with a grid-dependency wait (LayerNorm, the GEMMs, the small attention kernels, the arg-max
+    // reduction) may be launched while their predecessor still runs.  That pays for small shards, whose products run
+    // on the one-CTA GEMM and are short next to a launch:
+    // 0.201 -> 0.193 ms for a 10.8 M-parameter model on 32 x 128 tokens; with the CTA-pair GEMM of large shards it
+    // costs 1 %.  TLNN_PDL_PREFILL=1 / 0 forces it on / off.
+    static const int pdl_env = getenv("TLNN_PDL_PREFILL") ? (strcmp(getenv("TLNN_PDL_PREFILL"), "1") == 0 ? 1 : 0) : -1;
     const int d = m->d;
+    const bool pdl_auto = !tl_gemm_uses_pair(m->prec, (int)M, 3 * d, ctx->sm_count) && !tl_gemm_uses_pair(m->prec, (int)M, 4 * d, ctx->sm_count);
+    pdl_scope scope(ctx, (pdl_env < 0 ? pdl_auto : pdl_env == 1) && !ctx->prof_classes);
     const size_t stream_bytes = tl_ws_round((size_t)M * d * 4);
     const size_t tail = block_ws_bytes(m->prec, M, d);
     const size_t head = head_ws_bytes(ctx, m->prec, M, d, m->vocab, tokens != nullptr);

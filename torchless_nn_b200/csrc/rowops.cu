@@ -88,16 +88,32 @@ __global__ void embed_kernel(const void* __restrict__ ids, int ids_type, const f
 // ---- LayerNorm -----------------------------------------------------------------------------------------
 // One warp per row, the row held in registers (up to 32 x float4 per lane, d <= 4096): mean, then the mean of
 // squared deviations (the two-pass form NumPy's var uses), then (x - mean) / sqrt(var + eps) * gamma + beta.
-template <int KIND, int VPL /* float4 per lane */>
+// EARLY (a few rows, as in a decode step, where the kernel is pure latency): gamma and beta, which no predecessor
+// kernel writes, are loaded before the grid-dependency wait, so their latency overlaps the predecessor's tail.
+template <int KIND, int VPL /* float4 per lane */, bool EARLY = false>
 __global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                       const float* __restrict__ beta, float eps, void* __restrict__ out,
                                       long long rows, int d) {
-    tl_grid_dependency_sync();
     long long row = (long long)blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
     int lane = threadIdx.x % kWarp;
+    int nvec = d / 4;
+    float4 ge[EARLY ? VPL : 1], be[EARLY ? VPL : 1];
+    if (EARLY) {
+        tl_grid_dependency_trigger();
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            int c = i * kWarp + lane;
+            if (c < nvec) {
+                ge[i] = __ldg(reinterpret_cast<const float4*>(gamma) + c);
+                be[i] = __ldg(reinterpret_cast<const float4*>(beta) + c);
+            }
+        }
+        tl_grid_dependency_wait();
+    } else {
+        tl_grid_dependency_sync();
+    }
     if (row >= rows) return;
     const float4* src = reinterpret_cast<const float4*>(x + row * d);
-    int nvec = d / 4;
     float4 v[VPL];
     float s = 0.f;
 #pragma unroll
@@ -129,7 +145,9 @@ __global__ void layernorm_warp_kernel(const float* __restrict__ x, const float* 
     for (int i = 0; i < VPL; i++) {
         int c = i * kWarp + lane;
         if (c < nvec) {
-            float4 g = __ldg(g4 + c), b = __ldg(b4 + c);
+            float4 g, b;
+            if (EARLY) { g = ge[i]; b = be[i]; }
+            else { g = __ldg(g4 + c); b = __ldg(b4 + c); }
             float4 r;
             if (KIND == TL_OUT_BF16) {
                 // the result is rounded to 8 significant bits: one division per row and a multiplication per
@@ -466,7 +484,16 @@ static int layernorm_dispatch(tlnn_ctx* ctx, const float* x, const float* gamma,
 #define LN_CASE(V)                                                                                              \
     TL_LAUNCH(ctx, "layernorm", tl_launch_kernel(ctx, layernorm_warp_kernel<KIND, V>, dim3(grid), dim3(warps * 32), 0, \
                                                  x, gamma, beta, eps, out, rows, d))
-        if (vpl <= 1) LN_CASE(1);
+#define LN_EARLY(V)                                                                                             \
+    TL_LAUNCH(ctx, "layernorm", tl_launch_kernel(ctx, layernorm_warp_kernel<KIND, V, true>, dim3(grid), dim3(warps * 32), 0, \
+                                                 x, gamma, beta, eps, out, rows, d))
+        if (rows <= 1024 && vpl <= 8) {
+            if (vpl <= 2) LN_EARLY(2);
+            else if (vpl <= 4) LN_EARLY(4);
+            else if (vpl <= 6) LN_EARLY(6);
+            else LN_EARLY(8);
+        }
+        else if (vpl <= 1) LN_CASE(1);
         else if (vpl <= 2) LN_CASE(2);
         else if (vpl <= 4) LN_CASE(4);
         else if (vpl <= 6) LN_CASE(6);
@@ -474,6 +501,7 @@ static int layernorm_dispatch(tlnn_ctx* ctx, const float* x, const float* gamma,
         else if (vpl <= 16) LN_CASE(16);
         else LN_CASE(32);
 #undef LN_CASE
+#undef LN_EARLY
     } else {
         TL_LAUNCH(ctx, "layernorm", layernorm_block_kernel<KIND><<<(unsigned)rows, 256, 0, ctx->stream>>>(
                       x, gamma, beta, eps, out, rows, d));
