@@ -67,9 +67,10 @@ __global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const fl
 // cache rows [0, *len].  One CTA per (sequence, head); a group of HD*sizeof(E)/16 threads covers one key row with
 // 16-byte loads and the DA_THREADS threads cover DA_THREADS / group keys at a time.  One pass over the cache: a thread
 // requests the key rows AND the value rows of four keys before it uses the first, and every group keeps its own running
-// maximum, sum and weighted row (online softmax); the groups are merged through shared memory at the end.  The kernel
-// is a chain of round trips to L2 / HBM, so its time is the number of such rounds: the two-pass form (all scores, then
-// the maximum, then the values) needs twice as many and a score buffer as long as the cache.
+// maximum, sum and weighted row (online softmax); the groups are merged through shared memory at the end.  Nothing in
+// shared memory grows with the cache, so its length is bounded by the context only.  Measured on 64 sequences x 12
+// heads of 64 at 128-383 cached positions: one 16-byte load in flight per thread is 20 % slower per decode step, two
+// keys per round 9 % slower, eight 1.5 % slower; a two-pass form with a score buffer runs at the same speed.
 constexpr int DA_THREADS = 128;
 template <typename E, int HD>
 __global__ void __launch_bounds__(DA_THREADS)
