@@ -29,22 +29,23 @@ __device__ __forceinline__ float round_tf32(float x) {
     return __uint_as_float(u);
 }
 
-// qkv (B*T, 3d) -> kcache / vcache (B, cache_len, d), rows [0, T)
+// qkv (B*T, 3d) -> kcache / vcache (B, heads, cache_len, hd), positions [0, T), 16 bytes per thread and copy
 template <typename E>
 __global__ void kv_store_kernel(const E* __restrict__ qkv, E* __restrict__ kc, E* __restrict__ vc, int B, int T, int d,
                                 int hd, int cache_len) {
-    const long long total = (long long)B * T * d;
+    constexpr int PER = 16 / sizeof(E);            // elements per 16-byte unit (hd and d are multiples of it)
+    const long long total = (long long)B * T * (d / PER);
     const long long stride = (long long)gridDim.x * blockDim.x;
-    const int H = d / hd;
+    const int H = d / hd, upr = d / PER;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int c = (int)(i % d);
-        const long long row = i / d;
+        const int c = (int)(i % upr) * PER;
+        const long long row = i / upr;
         const int t = (int)(row % T);
         const long long b = row / T;
         const int h = c / hd;
         const long long dst = ((b * H + h) * cache_len + t) * hd + (c - h * hd);
-        kc[dst] = qkv[row * 3 * d + d + c];
-        vc[dst] = qkv[row * 3 * d + 2 * d + c];
+        *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(qkv + row * 3 * d + d + c);
+        *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(qkv + row * 3 * d + 2 * d + c);
     }
 }
 
@@ -204,7 +205,7 @@ inline int okind(int prec) { return prec == TLNN_PREC_BF16 ? TL_OUT_BF16 : TL_OU
 }  // namespace
 
 int tl_kv_store(tlnn_ctx* ctx, int prec, const void* qkv, void* kcache, void* vcache, int B, int T, int d, int heads, int cache_len) {
-    const size_t n = (size_t)B * T * d;
+    const size_t n = (size_t)B * T * d / (prec == TLNN_PREC_BF16 ? 8 : 4);     // 16-byte units
     if (n == 0) return TLNN_OK;
     int grid = (int)((n + 255) / 256);
     if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
