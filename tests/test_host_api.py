@@ -151,3 +151,40 @@ def test_basic_indexing_offsets_match_numpy_and_stay_selection_sized():
     big = Shape((64, 2048, 50257))                                                    # the predict(x)[0, -1] idiom
     got = DeviceArray._basic_offsets(big, (0, -1))
     assert got.shape == (50257,) and got[0] == 2047 * 50257
+
+
+def test_vit_recipe_is_recognised_only_when_it_is_the_recipe():
+    """The whole-model ViT call is taken only for VitProjector, [Dropout], encoder blocks of one width, LayerNorm,
+    VitMLPHead; anything else runs layer by layer.  Checked on stand-in layers (no device needed)."""
+    from torchless_nn_b200 import network
+    from torchless_nn_b200.network import ViTPlan
+
+    def stand_in(cls, **attrs):
+        obj = cls.__new__(cls)
+        obj.__dict__.update(attrs)
+        return obj
+
+    class Act:
+        def __init__(self, code): self.code = code
+        def act_code(self): return self.code
+
+    class Shape:
+        def __init__(self, *shape): self.shape = shape
+
+    def block(d, heads, decoder=False, act=1):
+        attn = type("A", (), {"embedding_dim": d, "num_heads": heads, "is_decoder": decoder})()
+        return stand_in(network.TransformerBlock, attn_block=attn, ffn=Act(act))
+
+    proj = stand_in(network.VitProjector, embedding_dim=192)
+    norm = stand_in(network.LayerNorm, gamma=Shape(192))
+    head = stand_in(network.VitMLPHead, weights=Shape(192, 10))
+    drop = stand_in(network.Dropout, dropout_rate=0.0, eval_mode=True)
+    good = [proj, drop, block(192, 6), block(192, 6), norm, head]
+    assert ViTPlan.match(good) is not None
+    assert ViTPlan.match([proj, norm, head]) is not None                        # no blocks at all
+    assert ViTPlan.match([proj, block(192, 6, decoder=True), norm, head]) is None   # a causal block is not the ViT recipe
+    assert ViTPlan.match([proj, block(192, 6), block(192, 3), norm, head]) is None  # blocks that differ
+    assert ViTPlan.match([proj, block(128, 4), norm, head]) is None                 # a width other than the projector's
+    assert ViTPlan.match([proj, block(192, 6), norm, stand_in(network.VitMLPHead, weights=Shape(128, 10))]) is None
+    assert ViTPlan.match([proj, block(192, 6), head]) is None                       # no final LayerNorm
+    assert ViTPlan.match(good[1:]) is None                                          # no projector
